@@ -1,0 +1,51 @@
+"""Plain batched fp32 matmul on the B200 tensor cores (drop-in for bmm.py:7 BMMCUDA)."""
+from __future__ import annotations
+
+import torch
+
+from .custom_kernel import CustomKernel, check, layout_letter, operand
+
+
+class BMMCUDA(CustomKernel):
+    """``BMMCUDA(patch_m, patch_n)(A, B) -> C`` with A [l,m,k] (or [m,k]) and B [l,k,n]
+    (or [k,n]), fp32 (bmm.py:8,68-129).
+
+    `patch_m` / `patch_n` sized the reference's CTA raster patch (bmm.py:19-21); they are
+    accepted and stored but never change results. Unlike the reference, which launched
+    its "nn" kernel for every stride layout (bmm.py:115), transposed views are honoured,
+    and the result lives on A's device rather than on cuda:0 (bmm.py:106)."""
+
+    def __init__(self, patch_m=4, patch_n=4):
+        super().__init__()
+        self.patch_m = patch_m
+        self.patch_n = patch_n
+
+    def get_mode(self, A, B):
+        """Stride layout of the last two dims, as bmm.py:56-66."""
+        mode = [None, None]
+        for i, X in enumerate((A, B)):
+            if X.stride()[-1] == 1:
+                mode[i] = "n"
+            elif X.stride()[-2] == 1:
+                mode[i] = "t"
+        return "".join(m or "?" for m in mode)
+
+    def __call__(self, A, B):
+        A3, B3, two_d = self.check_inputs(A, B)
+        l, m, k = A3.shape
+        n = B3.shape[2]
+        C = torch.empty((l, m, n), device=A3.device, dtype=torch.float32)
+        if l == 0 or m == 0 or n == 0:
+            return C[0] if two_d else C
+        if k == 0:
+            C.zero_()
+            return C[0] if two_d else C
+        a_keep, a_t, lda, sa = operand(A3)
+        b_keep, b_t, ldb, sb = operand(B3)
+        with torch.cuda.device(A3.device):
+            check(self.lib.fbmm_bmm_f32(
+                self.stream_ptr(A3.device),
+                a_keep.data_ptr(), layout_letter(a_t, False), lda, sa,
+                b_keep.data_ptr(), layout_letter(b_t, True), ldb, sb,
+                C.data_ptr(), n, m * n, l, m, n, k))
+        return C[0] if two_d else C

@@ -1,0 +1,496 @@
+// Host side of libfbmm.so: argument validation, tensor-map construction, work
+// decomposition and launches behind the C ABI declared in include/fbmm.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/fbmm.h"
+#include "fbmm_kernel.cuh"
+
+namespace {
+
+using namespace fbmm;
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define FBMM_CUDA(call)                                                                   \
+  do {                                                                                    \
+    cudaError_t e_ = (call);                                                              \
+    if (e_ != cudaSuccess) return fail(FBMM_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+  } while (0)
+
+// ---------------------------------------------------------------------------------------
+// per-device state
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+constexpr int kMaxDevices = 64;
+struct DeviceState {
+  bool ready = false;
+  int sms = 0;
+};
+std::mutex g_mu;
+DeviceState g_dev[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+
+constexpr int kStages = 3;
+constexpr int kTileN = 128;
+
+template <int EPI, int E>
+int set_smem_attr() {
+  using Traits = KernelTraits<kTileN, kStages, EPI, E>;
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<kTileN, kStages, EPI, E>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Traits::kSmemBytes)));
+  return FBMM_OK;
+}
+
+int device_state(DeviceState** out) {
+  int dev = 0;
+  FBMM_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(FBMM_ERR_INVALID, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mu);
+  DeviceState& st = g_dev[dev];
+  if (!st.ready) {
+    cudaDeviceProp prop;
+    FBMM_CUDA(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10)
+      return fail(FBMM_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", dev,
+                  prop.major, prop.minor);
+    if (g_encode == nullptr) {
+      void* fn = nullptr;
+      cudaDriverEntryPointQueryResult q;
+      FBMM_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+      if (fn == nullptr) return fail(FBMM_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    int rc;
+    if ((rc = set_smem_attr<kEpiStore, 1>()) != FBMM_OK) return rc;
+    if ((rc = set_smem_attr<kEpiMask, 1>()) != FBMM_OK) return rc;
+    if ((rc = set_smem_attr<kEpiMin, 1>()) != FBMM_OK) return rc;
+    if ((rc = set_smem_attr<kEpiTopk, 4>()) != FBMM_OK) return rc;
+    if ((rc = set_smem_attr<kEpiTopk, 8>()) != FBMM_OK) return rc;
+    st.sms = prop.multiProcessorCount;
+    st.ready = true;
+  }
+  *out = &st;
+  return FBMM_OK;
+}
+
+// SM count for the workspace queries; falls back to the B200 figure when no device can
+// be asked (the queries must work on a machine without a GPU).
+int sm_count_or_default() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 148; }
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+    cudaGetLastError();
+    return 148;
+  }
+  return sms;
+}
+
+// ---------------------------------------------------------------------------------------
+// operands
+// ---------------------------------------------------------------------------------------
+struct Operand {
+  const float* ptr;
+  bool mn_major;     // contiguous along M/N (true) or along K (false)
+  long long ld;      // pitch of stored rows (elements)
+  long long stride;  // batch stride (elements)
+  int rows;          // M or N
+};
+
+int check_operand(const char* name, const Operand& op, int k, int l) {
+  if (op.ptr == nullptr) return fail(FBMM_ERR_INVALID, "%s is null", name);
+  const long long inner = op.mn_major ? op.rows : k;
+  if (op.ld < inner) return fail(FBMM_ERR_INVALID, "%s pitch %lld smaller than its row length %lld", name, op.ld, inner);
+  if ((reinterpret_cast<uintptr_t>(op.ptr) & 15u) != 0) return fail(FBMM_ERR_ALIGN, "%s is not 16-byte aligned", name);
+  if ((op.ld & 3) != 0) return fail(FBMM_ERR_ALIGN, "%s pitch %lld is not a multiple of 4 elements", name, op.ld);
+  if (l > 1 && (op.stride & 3) != 0)
+    return fail(FBMM_ERR_ALIGN, "%s batch stride %lld is not a multiple of 4 elements", name, op.stride);
+  if (l > 1 && op.stride < 0) return fail(FBMM_ERR_INVALID, "%s batch stride is negative", name);
+  return FBMM_OK;
+}
+
+// 3-D tiled tensor map over one operand. K-major: dims (k, rows, l), box (32, box_rows, 1),
+// 128-byte swizzle. MN-major: dims (rows, k, l), box (32, 32, 1), 128-byte swizzle with
+// 32-byte atoms (the only MN-major layout tcgen05 takes for tf32).
+int make_tensor_map(CUtensorMap* map, const Operand& op, int k, int l, int box_rows) {
+  cuuint64_t dims[3];
+  cuuint32_t box[3];
+  if (op.mn_major) {
+    dims[0] = static_cast<cuuint64_t>(op.rows);
+    dims[1] = static_cast<cuuint64_t>(k);
+    box[0] = 32; box[1] = 32;
+  } else {
+    dims[0] = static_cast<cuuint64_t>(k);
+    dims[1] = static_cast<cuuint64_t>(op.rows);
+    box[0] = 32; box[1] = static_cast<cuuint32_t>(box_rows);
+  }
+  dims[2] = static_cast<cuuint64_t>(l);
+  box[2] = 1;
+  const cuuint64_t pitch_bytes = static_cast<cuuint64_t>(op.ld) * 4u;
+  cuuint64_t strides[2] = {pitch_bytes, l > 1 ? static_cast<cuuint64_t>(op.stride) * 4u : pitch_bytes * dims[1]};
+  if (strides[1] == 0) strides[1] = pitch_bytes;  // broadcast batch: any legal value, coordinate stays 0
+  cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(op.ptr), dims, strides,
+                              box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FBMM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return FBMM_OK;
+}
+
+int parse_layout(int letter, bool* transposed) {
+  if (letter == 'n' || letter == 'N') { *transposed = false; return FBMM_OK; }
+  if (letter == 't' || letter == 'T') { *transposed = true; return FBMM_OK; }
+  return fail(FBMM_ERR_INVALID, "layout must be 'n' or 't', got %d", letter);
+}
+
+int check_dims(int l, int m, int n, int k) {
+  if (l <= 0 || m <= 0 || n <= 0 || k <= 0)
+    return fail(FBMM_ERR_INVALID, "l, m, n, k must be positive, got %d %d %d %d", l, m, n, k);
+  return FBMM_OK;
+}
+
+// A problem in "row" form: rows come from operand `a` (M of them), columns from `b`.
+struct RowProblem {
+  Operand a, b;
+  int L, M, N, K;
+};
+
+// Builds the row-form problem of the reference's (A, B, dim) call. dim == 2 reduces over
+// the columns of A @ B; dim == 1 reduces over its rows, which is the row-wise reduction of
+// B^T @ A^T: the operands swap and their storage is reread with the other majorness.
+int make_row_problem(RowProblem* p, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
+                     int b_layout, long long ldb, long long stride_b, int l, int m, int n, int k, int dim) {
+  bool at, bt;
+  int rc;
+  if ((rc = parse_layout(a_layout, &at)) != FBMM_OK) return rc;
+  if ((rc = parse_layout(b_layout, &bt)) != FBMM_OK) return rc;
+  // storage majorness of the two matrices as given
+  const Operand opA{A, at, lda, stride_a, m};   // 'n': [m][k] K-major; 't': [k][m] MN-major
+  const Operand opB{B, !bt, ldb, stride_b, n};  // 'n': [k][n] MN-major; 't': [n][k] K-major
+  if (dim == 2) {
+    p->a = opA; p->b = opB; p->M = m; p->N = n;
+  } else if (dim == 1) {
+    p->a = opB; p->b = opA; p->M = n; p->N = m;
+  } else {
+    return fail(FBMM_ERR_INVALID, "dim must be 1 or 2 (counted on the 3-D product), got %d", dim);
+  }
+  p->L = l; p->K = k;
+  return FBMM_OK;
+}
+
+// Column chunking: with few row blocks, split the column sweep so that every SM has
+// work. Picks the chunk count with the smallest modelled makespan; `overhead_tiles` is
+// the cost of one extra unit in tile-times.
+void choose_chunks(int L, int m_blocks, int n_tiles, int sms, int overhead_tiles, int max_chunks, int* n_chunks,
+                   int* tiles_per_chunk) {
+  const long long base = static_cast<long long>(L) * m_blocks;
+  long long best_cost = -1;
+  int best_c = 1, best_tpc = n_tiles;
+  const int limit = n_tiles < max_chunks ? n_tiles : max_chunks;
+  for (int c = 1; c <= limit; ++c) {
+    const int tpc = (n_tiles + c - 1) / c;
+    const int cc = (n_tiles + tpc - 1) / tpc;
+    const long long units = base * cc;
+    const long long waves = (units + sms - 1) / sms;
+    const long long cost = waves * (tpc + overhead_tiles);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_c = cc; best_tpc = tpc; }
+  }
+  *n_chunks = best_c;
+  *tiles_per_chunk = best_tpc;
+}
+
+constexpr int kMinOverheadTiles = 1;
+constexpr int kTopkOverheadTiles = 12;
+constexpr int kMaxChunks = 64;
+
+template <int EPI, int E>
+int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p, GemmShape shape, const EpiArgs& epi) {
+  using Traits = KernelTraits<kTileN, kStages, EPI, E>;
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = make_tensor_map(&ta, p.a, p.K, p.L, kTileM)) != FBMM_OK) return rc;
+  if ((rc = make_tensor_map(&tb, p.b, p.K, p.L, kTileN)) != FBMM_OK) return rc;
+  const long long grid = shape.num_units < st.sms ? shape.num_units : st.sms;
+  fbmm_gemm_kernel<kTileN, kStages, EPI, E>
+      <<<static_cast<unsigned>(grid), kNumThreads, Traits::kSmemBytes, stream>>>(ta, tb, shape, epi);
+  FBMM_CUDA(cudaGetLastError());
+  return FBMM_OK;
+}
+
+GemmShape base_shape(const RowProblem& p) {
+  GemmShape s{};
+  s.L = p.L; s.M = p.M; s.N = p.N; s.K = p.K;
+  s.a_mn = p.a.mn_major ? 1 : 0;
+  s.b_mn = p.b.mn_major ? 1 : 0;
+  s.m_blocks = (p.M + kTileM - 1) / kTileM;
+  s.n_tiles = (p.N + kTileN - 1) / kTileN;
+  return s;
+}
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace
+
+// =======================================================================================
+// C ABI
+// =======================================================================================
+extern "C" {
+
+int fbmm_version(void) { return 1000; }
+
+const char* fbmm_last_error(void) { return g_err; }
+
+int fbmm_check(void* stream) {
+  FBMM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  unsigned int status[4] = {0, 0, 0, 0};
+  FBMM_CUDA(cudaMemcpyFromSymbol(status, fbmm::g_fbmm_status, sizeof(status)));
+  if (status[0] != 0) {
+    const unsigned int zero[4] = {0, 0, 0, 0};
+    FBMM_CUDA(cudaMemcpyToSymbol(fbmm::g_fbmm_status, zero, sizeof(zero)));
+    return fail(FBMM_ERR_DEVICE, "a kernel gave up on a bounded wait (status 0x%x)", status[0]);
+  }
+  return FBMM_OK;
+}
+
+int fbmm_bmm_f32(void* stream, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
+                 int b_layout, long long ldb, long long stride_b, float* C, long long ldc, long long stride_c, int l,
+                 int m, int n, int k) {
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if (C == nullptr) return fail(FBMM_ERR_INVALID, "C is null");
+  if (ldc < n) return fail(FBMM_ERR_INVALID, "ldc %lld smaller than n %d", ldc, n);
+  RowProblem p;
+  if ((rc = make_row_problem(&p, A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, l, m, n, k, 2)) != FBMM_OK) return rc;
+  if ((rc = check_operand("A", p.a, k, l)) != FBMM_OK) return rc;
+  if ((rc = check_operand("B", p.b, k, l)) != FBMM_OK) return rc;
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape(p);
+  s.n_chunks = s.n_tiles;
+  s.tiles_per_chunk = 1;
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  EpiArgs e{};
+  e.C = C; e.ldc = ldc; e.stride_c = stride_c;
+  return launch_gemm<kEpiStore, 1>(static_cast<cudaStream_t>(stream), *st, p, s, e);
+}
+
+int fbmm_mbmm_f32(void* stream, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
+                  int b_layout, long long ldb, long long stride_b, float* C, long long ldc, long long stride_c,
+                  const unsigned char* block_mask, const unsigned char* thread_mask,
+                  const unsigned char* element_mask, int share_mask, int l, int m, int n, int k) {
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if (C == nullptr) return fail(FBMM_ERR_INVALID, "C is null");
+  if (ldc < n) return fail(FBMM_ERR_INVALID, "ldc %lld smaller than n %d", ldc, n);
+  if (block_mask == nullptr || thread_mask == nullptr || element_mask == nullptr)
+    return fail(FBMM_ERR_INVALID, "a mask pointer is null");
+  RowProblem p;
+  if ((rc = make_row_problem(&p, A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, l, m, n, k, 2)) != FBMM_OK) return rc;
+  if ((rc = check_operand("A", p.a, k, l)) != FBMM_OK) return rc;
+  if ((rc = check_operand("B", p.b, k, l)) != FBMM_OK) return rc;
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape(p);
+  s.n_chunks = s.n_tiles;
+  s.tiles_per_chunk = 1;
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  EpiArgs e{};
+  e.C = C; e.ldc = ldc; e.stride_c = stride_c;
+  e.block_mask = block_mask; e.thread_mask = thread_mask; e.element_mask = element_mask;
+  e.bm_cols = (n + 127) / 128;
+  e.tm_cols = (n + 7) / 8;
+  e.bm_stride = share_mask ? 0 : static_cast<long long>((m + 127) / 128) * e.bm_cols;
+  e.tm_stride = share_mask ? 0 : static_cast<long long>((m + 7) / 8) * e.tm_cols;
+  e.em_stride = share_mask ? 0 : static_cast<long long>(m) * n;
+  return launch_gemm<kEpiMask, 1>(static_cast<cudaStream_t>(stream), *st, p, s, e);
+}
+
+size_t fbmm_min_bmm_workspace_bytes(int l, int m, int n, int k, int dim) {
+  (void)k;
+  if (l <= 0 || m <= 0 || n <= 0) return 0;
+  const long long rows = static_cast<long long>(l) * (dim == 1 ? n : m);
+  return static_cast<size_t>(rows) * sizeof(unsigned long long);
+}
+
+int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
+                     int b_layout, long long ldb, long long stride_b, float* values, long long* indices, int l, int m,
+                     int n, int k, int dim, void* workspace, size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
+  RowProblem p;
+  if ((rc = make_row_problem(&p, A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
+  if ((rc = check_operand("A", dim == 2 ? p.a : p.b, k, l)) != FBMM_OK) return rc;
+  if ((rc = check_operand("B", dim == 2 ? p.b : p.a, k, l)) != FBMM_OK) return rc;
+  const size_t need = fbmm_min_bmm_workspace_bytes(l, m, n, k, dim);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(FBMM_ERR_WORKSPACE, "min_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 7u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 8-byte aligned");
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape(p);
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  const long long rows = static_cast<long long>(l) * p.M;
+  unsigned long long* keys = static_cast<unsigned long long*>(workspace);
+  FBMM_CUDA(cudaMemsetAsync(keys, 0xff, static_cast<size_t>(rows) * 8, stream));
+  EpiArgs e{};
+  e.keys = keys;
+  if ((rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e)) != FBMM_OK) return rc;
+  const int threads = 256;
+  const long long blocks = (rows + threads - 1) / threads;
+  fbmm_min_finalize_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(keys, values, indices, rows);
+  FBMM_CUDA(cudaGetLastError());
+  return FBMM_OK;
+}
+
+static void topk_plan(int l, int rows_per_batch, int cols, int sms, int* n_chunks, int* tiles_per_chunk) {
+  const int m_blocks = (rows_per_batch + kTileM - 1) / kTileM;
+  const int n_tiles = (cols + kTileN - 1) / kTileN;
+  choose_chunks(l, m_blocks, n_tiles, sms, kTopkOverheadTiles, kMaxChunks, n_chunks, tiles_per_chunk);
+}
+
+size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim) {
+  (void)k;
+  if (l <= 0 || m <= 0 || n <= 0 || topk <= 0) return 0;
+  const int rows_pb = dim == 1 ? n : m, cols = dim == 1 ? m : n;
+  int n_chunks, tpc;
+  topk_plan(l, rows_pb, cols, sm_count_or_default(), &n_chunks, &tpc);
+  if (n_chunks <= 1) return 0;
+  const size_t entries = static_cast<size_t>(n_chunks) * l * rows_pb * topk;
+  return align_up(entries * sizeof(float), 256) + entries * sizeof(long long);
+}
+
+int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long* cand_indices, int groups,
+                        long long rows, int topk, float* out_values, long long* out_indices);
+
+int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
+                      int b_layout, long long ldb, long long stride_b, float* values, long long* indices, int l, int m,
+                      int n, int k, int topk, int dim, long long index_offset, void* workspace,
+                      size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
+  if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
+  RowProblem p;
+  if ((rc = make_row_problem(&p, A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
+  if ((rc = check_operand("A", dim == 2 ? p.a : p.b, k, l)) != FBMM_OK) return rc;
+  if ((rc = check_operand("B", dim == 2 ? p.b : p.a, k, l)) != FBMM_OK) return rc;
+  if (static_cast<long long>(p.N) + index_offset > 0x7ffffffell || index_offset < 0)
+    return fail(FBMM_ERR_INVALID, "column indices (offset %lld + %d columns) must stay below 2^31 - 1", index_offset, p.N);
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape(p);
+  topk_plan(l, p.M, p.N, st->sms, &s.n_chunks, &s.tiles_per_chunk);
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  const long long rows = static_cast<long long>(l) * p.M;
+  EpiArgs e{};
+  e.k = topk;
+  e.index_offset = index_offset;
+  if (s.n_chunks > 1) {
+    const size_t entries = static_cast<size_t>(s.n_chunks) * rows * topk;
+    const size_t need = align_up(entries * sizeof(float), 256) + entries * sizeof(long long);
+    if (workspace == nullptr || workspace_bytes < need)
+      return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+      return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
+    e.topk_values = static_cast<float*>(workspace);
+    e.topk_indices = reinterpret_cast<long long*>(static_cast<char*>(workspace) + align_up(entries * sizeof(float), 256));
+    e.topk_chunk_rows = rows;
+  } else {
+    e.topk_values = values;
+    e.topk_indices = indices;
+    e.topk_chunk_rows = 0;
+  }
+  if (topk <= 96) rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e);
+  else rc = launch_gemm<kEpiTopk, 8>(stream, *st, p, s, e);
+  if (rc != FBMM_OK) return rc;
+  if (s.n_chunks > 1)
+    return fbmm_topk_merge_f32(stream_, e.topk_values, e.topk_indices, s.n_chunks, rows, topk, values, indices);
+  return FBMM_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// candidate merge (one warp per row)
+// ---------------------------------------------------------------------------------------
+namespace fbmm {
+
+template <int E>
+__global__ void __launch_bounds__(128) fbmm_topk_merge_kernel(const float* __restrict__ cv, const long long* __restrict__ ci,
+                                                              int groups, long long rows, int k, float* __restrict__ ov,
+                                                              long long* __restrict__ oi) {
+  const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;  // whole warps leave together
+  const int lane = static_cast<int>(lane_id());
+  float v[E];
+  int ix[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) { v[j] = -INFINITY; ix[j] = kTopkEmpty; }
+  // slots [0, k): running best; slots [k, 2k): next group's list
+  for (int g = 0; g < groups; ++g) {
+    const float* gv = cv + (static_cast<long long>(g) * rows + row) * k;
+    const long long* gi = ci + (static_cast<long long>(g) * rows + row) * k;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      const int i = j * 32 + lane;
+      if (i >= k) {
+        v[j] = -INFINITY;
+        ix[j] = kTopkEmpty;
+        if (i < 2 * k) {
+          const long long id = gi[i - k];
+          if (id >= 0) { v[j] = gv[i - k]; ix[j] = static_cast<int>(id); }
+        }
+      }
+    }
+    warp_bitonic_sort_desc<E>(v, ix);
+  }
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const int i = j * 32 + lane;
+    if (i < k) {
+      ov[row * k + i] = v[j];
+      oi[row * k + i] = (ix[j] == kTopkEmpty) ? -1ll : static_cast<long long>(ix[j]);
+    }
+  }
+}
+
+}  // namespace fbmm
+
+extern "C" int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long* cand_indices, int groups,
+                                   long long rows, int topk, float* out_values, long long* out_indices) {
+  if (cand_values == nullptr || cand_indices == nullptr || out_values == nullptr || out_indices == nullptr)
+    return fail(FBMM_ERR_INVALID, "a pointer is null");
+  if (groups <= 0 || rows <= 0) return fail(FBMM_ERR_INVALID, "groups and rows must be positive");
+  if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
+  const long long blocks = (rows + 3) / 4;
+  if (blocks > 0x7fffffffll) return fail(FBMM_ERR_INVALID, "too many rows");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (2 * topk <= 128)
+    fbmm::fbmm_topk_merge_kernel<4><<<static_cast<unsigned>(blocks), 128, 0, s>>>(cand_values, cand_indices, groups, rows, topk, out_values, out_indices);
+  else
+    fbmm::fbmm_topk_merge_kernel<8><<<static_cast<unsigned>(blocks), 128, 0, s>>>(cand_values, cand_indices, groups, rows, topk, out_values, out_indices);
+  FBMM_CUDA(cudaGetLastError());
+  return FBMM_OK;
+}

@@ -1,0 +1,65 @@
+"""Fused matmul + min/argmin (drop-in for minbmm.py:7 MinBMMCUDA)."""
+from __future__ import annotations
+
+import torch
+
+from .custom_kernel import CustomKernel, check, layout_letter, operand
+
+
+class MinBMMCUDA(CustomKernel):
+    """``MinBMMCUDA(patch_m, patch_n, distance)(A, B, dim) -> (values, indices)``.
+
+    A [l,m,k] @ B [l,k,n] is reduced with min/argmin along `dim` of the 3-D product
+    without ever being written out: dim=1 gives [l,n], dim=2 gives [l,m]
+    (minbmm.py:116-121); for 2-D inputs `dim` is bumped by one first (minbmm.py:86-90).
+    values are fp32, indices int64. Ties resolve to the lowest index (the reference is
+    racy there, kernels/minbmm.cu:76-79). Only distance="inner" is implemented."""
+
+    def __init__(self, patch_m=4, patch_n=4, distance="inner"):
+        super().__init__()
+        self.patch_m = patch_m
+        self.patch_n = patch_n
+        if distance == "inner":
+            pass
+        elif distance in ("l2", "euclidean", "l1", "manhattan"):
+            raise NotImplementedError(f"distance={distance!r} is not implemented; only 'inner' is")
+        else:
+            raise ValueError("Unrecognized distance type")  # minbmm.py:19 builds this but never raises it
+        self.distance = distance
+
+    def get_mode(self, A, B):
+        mode = [None, None]
+        for i, X in enumerate((A, B)):
+            if X.stride()[-1] == 1:
+                mode[i] = "n"
+            elif X.stride()[-2] == 1:
+                mode[i] = "t"
+        return "".join(m or "?" for m in mode)
+
+    def __call__(self, A, B, dim=1):
+        A3, B3, two_d = self.check_inputs(A, B)
+        if two_d:
+            dim += 1
+        if dim not in (1, 2):
+            raise ValueError("dim must be 1 or 2 on the 3-D product (0 or 1 for 2-D inputs)")
+        l, m, k = A3.shape
+        n = B3.shape[2]
+        if min(l, m, n, k) <= 0:
+            raise ValueError(f"empty problem: l={l} m={m} n={n} k={k}")
+        rows = n if dim == 1 else m
+        values = torch.empty((l, rows), device=A3.device, dtype=torch.float32)
+        indices = torch.empty((l, rows), device=A3.device, dtype=torch.int64)
+        a_keep, a_t, lda, sa = operand(A3)
+        b_keep, b_t, ldb, sb = operand(B3)
+        ws_bytes = self.lib.fbmm_min_bmm_workspace_bytes(l, m, n, k, dim)
+        ws = torch.empty(max(ws_bytes, 8), device=A3.device, dtype=torch.uint8)
+        with torch.cuda.device(A3.device):
+            check(self.lib.fbmm_min_bmm_f32(
+                self.stream_ptr(A3.device),
+                a_keep.data_ptr(), layout_letter(a_t, False), lda, sa,
+                b_keep.data_ptr(), layout_letter(b_t, True), ldb, sb,
+                values.data_ptr(), indices.data_ptr(), l, m, n, k, dim,
+                ws.data_ptr(), ws_bytes))
+        if two_d:
+            return values[0], indices[0]
+        return values, indices

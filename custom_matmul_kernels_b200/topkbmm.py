@@ -1,0 +1,68 @@
+"""Fused matmul + top-k (drop-in for topkbmm.py:7 TopkBMMCUDA)."""
+from __future__ import annotations
+
+import torch
+
+from .custom_kernel import CustomKernel, check, layout_letter, operand
+
+
+class TopkBMMCUDA(CustomKernel):
+    """``TopkBMMCUDA(patch_m, patch_n, distance)(A, B, k, dim) -> (values, indices)``.
+
+    The k largest entries, descending, along `dim` of A [l,m,k] @ B [l,k,n], never
+    writing the product out. k is always the LAST output axis: dim=1 gives [l,n,k], dim=2
+    gives [l,m,k] (topkbmm.py:119-127) -- not torch.topk's layout for dim=1. 0 < k <= 128
+    (topkbmm.py:104). Outputs are contiguous (the reference returns [:,:,:k] views of
+    128-wide buffers, topkbmm.py:150-151). Any m and n are handled; where fewer than k
+    entries exist the tail is -inf / -1. Only distance="inner" is implemented."""
+
+    def __init__(self, patch_m=4, patch_n=4, distance="inner"):
+        super().__init__()
+        self.patch_m = patch_m
+        self.patch_n = patch_n
+        if distance == "inner":
+            pass
+        elif distance in ("l2", "euclidean", "l1", "manhattan"):
+            raise NotImplementedError(f"distance={distance!r} is not implemented; only 'inner' is")
+        else:
+            raise ValueError("Unrecognized distance type")
+        self.distance = distance
+
+    def get_mode(self, A, B):
+        mode = [None, None]
+        for i, X in enumerate((A, B)):
+            if X.stride()[-1] == 1:
+                mode[i] = "n"
+            elif X.stride()[-2] == 1:
+                mode[i] = "t"
+        return "".join(m or "?" for m in mode)
+
+    def __call__(self, A, B, k=128, dim=1, index_offset=0):
+        A3, B3, two_d = self.check_inputs(A, B)
+        if two_d:
+            dim += 1
+        if dim not in (1, 2):
+            raise ValueError("dim must be 1 or 2 on the 3-D product (0 or 1 for 2-D inputs)")
+        if not 0 < k <= 128:
+            raise ValueError("k must be in 1..128")
+        l, m, d = A3.shape
+        n = B3.shape[2]
+        if min(l, m, n, d) <= 0:
+            raise ValueError(f"empty problem: l={l} m={m} n={n} k={d}")
+        rows = n if dim == 1 else m
+        values = torch.empty((l, rows, k), device=A3.device, dtype=torch.float32)
+        indices = torch.empty((l, rows, k), device=A3.device, dtype=torch.int64)
+        a_keep, a_t, lda, sa = operand(A3)
+        b_keep, b_t, ldb, sb = operand(B3)
+        with torch.cuda.device(A3.device):
+            ws_bytes = self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim)
+            ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
+            check(self.lib.fbmm_topk_bmm_f32(
+                self.stream_ptr(A3.device),
+                a_keep.data_ptr(), layout_letter(a_t, False), lda, sa,
+                b_keep.data_ptr(), layout_letter(b_t, True), ldb, sb,
+                values.data_ptr(), indices.data_ptr(), l, m, n, d, k, dim, index_offset,
+                ws.data_ptr(), ws_bytes))
+        if two_d:
+            return values[0], indices[0]
+        return values, indices

@@ -1,0 +1,122 @@
+/* fbmm.h -- C ABI of libfbmm.so, the sm_100a fused fp32 batched-matmul library.
+ *
+ * This is the boundary that replaces the reference's CuPy RawKernel launches
+ * (custom_kernel.py:12-43 and the `cp.RawKernel(...)(grid, block, args, stream)` calls in
+ * bmm.py:115-125, mbmm.py:83-97, minbmm.py:132-143, topkbmm.py:137-148): plain pointers
+ * and sizes in, status code out, no torch or CuPy types.
+ *
+ * Conventions shared by every entry point
+ *  - All pointers are device pointers on the CURRENT CUDA device; `stream` is a
+ *    cudaStream_t passed as void* (0 = default stream). Calls only enqueue work.
+ *  - Logical shapes are the reference's: A is [l, m, k], B is [l, k, n] (bmm.py:86-87).
+ *    `a_layout` / `b_layout` are 'n' or 't', the suffix letters of the reference kernels
+ *    (kernels/bmm.cu:185,94,2,277): A 'n' is stored [l][m][k], A 't' is stored [l][k][m];
+ *    B 'n' is stored [l][k][n], B 't' is stored [l][n][k] (kernels/bmm_helpers.cu:263,311,
+ *    275,323). `ld*` is the pitch, in elements, between consecutive stored rows and
+ *    `stride_*` the distance, in elements, between consecutive batches.
+ *  - TMA requirements: operand base pointers 16-byte aligned, pitches and batch strides
+ *    multiples of 4 elements. Violations return FBMM_ERR_ALIGN (the Python wrappers
+ *    repack such operands before calling).
+ *  - The library allocates no memory. Scratch comes from the caller through
+ *    `workspace` / `workspace_bytes`, sized by the matching *_workspace_bytes query.
+ *  - Return value: FBMM_OK or a negative FBMM_ERR_* code; fbmm_last_error() gives the
+ *    message of the calling thread's last failure. Nothing throws, aborts or traps.
+ */
+#ifndef FBMM_H_
+#define FBMM_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FBMM_OK 0
+#define FBMM_ERR_INVALID (-1)     /* bad shape, layout letter, dim, k, null pointer */
+#define FBMM_ERR_ALIGN (-2)       /* pointer or pitch breaks the TMA alignment rules */
+#define FBMM_ERR_WORKSPACE (-3)   /* workspace missing or too small */
+#define FBMM_ERR_CUDA (-4)        /* a CUDA runtime / driver call failed */
+#define FBMM_ERR_DEVICE (-5)      /* a kernel reported a bounded wait that ran out */
+#define FBMM_ERR_UNSUPPORTED (-6) /* not an sm_100 device */
+
+/* Library version (major * 1000 + minor). No reference counterpart. */
+int fbmm_version(void);
+
+/* Message of the calling thread's last failed call ("" if none). Replaces the Python
+ * exceptions CuPy raised on launch failure (no explicit reference line). */
+const char* fbmm_last_error(void);
+
+/* Reads and clears the device status word of the current device after synchronising
+ * `stream`. FBMM_ERR_DEVICE if a kernel gave up on a wait since the last check. The
+ * reference has no counterpart (its spin mutex silently proceeds unlocked,
+ * kernels/topkbmm.cu:23). */
+int fbmm_check(void* stream);
+
+/* C[l,m,n] = A @ B, fp32 in, fp32 out (3xTF32 on the tensor cores).
+ * Replaces bmm_nn / bmm_nt / bmm_tn / bmm_tt (kernels/bmm.cu:185,94,2,277), launched from
+ * BMMCUDA.__call__ (bmm.py:68-125). C is written completely (no pre-zeroing needed). */
+int fbmm_bmm_f32(void* stream,
+                 const float* A, int a_layout, long long lda, long long stride_a,
+                 const float* B, int b_layout, long long ldb, long long stride_b,
+                 float* C, long long ldc, long long stride_c,
+                 int l, int m, int n, int k);
+
+/* Masked bmm. Replaces mbmm_nn (kernels/mbmm.cu:209-374), launched from
+ * MBMMCUDA._call_nn (mbmm.py:52-98). Masks are uint8: block_mask [l, ceil(m/128),
+ * ceil(n/128)] (0 = the 128x128 tile is neither loaded nor multiplied and C is 0 there,
+ * kernels/mbmm.cu:251-255), thread_mask [l, ceil(m/8), ceil(n/8)] (0 = that 8x8 tile of C
+ * is 0, kernels/mbmm.cu:360-363), element_mask [l, m, n] (C is multiplied by the byte,
+ * kernels/mbmm.cu:111-133). With share_mask != 0 the masks have no batch axis and serve
+ * every batch (mbmm.py:65-68). C is written completely, zeros included. */
+int fbmm_mbmm_f32(void* stream,
+                  const float* A, int a_layout, long long lda, long long stride_a,
+                  const float* B, int b_layout, long long ldb, long long stride_b,
+                  float* C, long long ldc, long long stride_c,
+                  const unsigned char* block_mask, const unsigned char* thread_mask,
+                  const unsigned char* element_mask, int share_mask,
+                  int l, int m, int n, int k);
+
+/* Row-wise (dim = 2, output [l, m]) or column-wise (dim = 1, output [l, n]) minimum and
+ * argmin of A @ B without materialising the product. Replaces min_bmm_nn/nt/tn/tt
+ * (kernels/minbmm.cu:348,252,156,443) with their epilogues min_dim_2 / min_dim_1
+ * (kernels/minbmm.cu:86,13), launched from MinBMMCUDA.__call__ (minbmm.py:78-143).
+ * `dim` counts on the 3-D product as in minbmm.py:100,116-121. Ties: lowest index.
+ * values fp32, indices int64; neither needs initialising. */
+size_t fbmm_min_bmm_workspace_bytes(int l, int m, int n, int k, int dim);
+int fbmm_min_bmm_f32(void* stream,
+                     const float* A, int a_layout, long long lda, long long stride_a,
+                     const float* B, int b_layout, long long ldb, long long stride_b,
+                     float* values, long long* indices,
+                     int l, int m, int n, int k, int dim,
+                     void* workspace, size_t workspace_bytes);
+
+/* Largest-`topk` entries (descending) and their indices per row (dim = 2, output
+ * [l, m, topk]) or per column (dim = 1, output [l, n, topk]) of A @ B. Replaces
+ * topk_bmm_nn/nt/tn/tt (kernels/topkbmm.cu:500,403,306,597) with topk_dim_2 / topk_dim_1
+ * (kernels/topkbmm.cu:249,193), launched from TopkBMMCUDA.__call__ (topkbmm.py:81-157).
+ * 0 < topk <= 128 (topkbmm.py:104). Outputs are contiguous [.., topk] (the reference
+ * returns [:, :, :k] views of 128-wide buffers, topkbmm.py:150-151). If fewer than topk
+ * entries exist the tail is -inf / -1 (kernels/topkbmm.cu:277-278). `index_offset` is
+ * added to every index written (used when B holds a column shard). */
+size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim);
+int fbmm_topk_bmm_f32(void* stream,
+                      const float* A, int a_layout, long long lda, long long stride_a,
+                      const float* B, int b_layout, long long ldb, long long stride_b,
+                      float* values, long long* indices,
+                      int l, int m, int n, int k, int topk, int dim,
+                      long long index_offset,
+                      void* workspace, size_t workspace_bytes);
+
+/* Merges `groups` descending candidate lists per row, cand_values / cand_indices laid
+ * out [groups][rows][topk] (index -1 = empty slot), into the `topk` largest per row.
+ * The stand-alone analogue of the reference's `bitonic_sort` kernel
+ * (kernels/bitonic_sort.cu:183-216), used after column-sharded top-k. */
+int fbmm_topk_merge_f32(void* stream,
+                        const float* cand_values, const long long* cand_indices,
+                        int groups, long long rows, int topk,
+                        float* out_values, long long* out_indices);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FBMM_H_ */
