@@ -1,0 +1,492 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-BMM hot path on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--impl reference]
+
+Prints ONE JSON line (rank 0). Workloads are the five benchmark configurations:
+  c1 min_bmm  A[1,16384,64]    B[1,64,16384]            rows sharded
+  c2 bmm      A[128,1024,128]  B[128,128,1024]          batches sharded
+  c3 mbmm     A[128,1024,64]   B[128,64,1024] + mask    batches sharded
+  c4 min_bmm  A[1,1048576,128] B[1,128,65536]           rows sharded      (default)
+  c5 topk_bmm A[1,1048576,256] B[1,256,1048576], k=64   B columns sharded + all-gather + merge
+A step is one pass of the op over the whole configuration (strong scaling: the
+configuration is fixed, each rank takes its shard). Inputs are seeded synthetic tensors
+generated on the host. `value` is timed with the shard resident in HBM; `e2e` runs the
+same step through the Python wrapper from pinned host buffers, host<->device copies
+inside the timed region. `--impl reference` times the reference's semantics on the host
+cores (torch.bmm + min / topk / masked_fill, the reference's own test expressions) on a
+bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+L2_BYTES = 126 * 1024 * 1024
+
+SHAPES = {  # l, m, k, n
+    "c1": (1, 16384, 64, 16384),
+    "c2": (128, 1024, 128, 1024),
+    "c3": (128, 1024, 64, 1024),
+    "c4": (1, 1048576, 128, 65536),
+    "c5": (1, 1048576, 256, 1048576),
+}
+SEEDS = {"c1": 1001, "c2": 1002, "c3": 1003, "c4": 1004, "c5": 1005}
+OPS = {"c1": "min_bmm", "c2": "bmm", "c3": "mbmm", "c4": "min_bmm", "c5": "topk_bmm"}
+TOPK = 64
+
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+# ---------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            p = [x.strip() for x in ln.split(",")]
+            if len(p) < 7:
+                continue
+            try:
+                sm.append(float(p[0]))
+                mx.append(float(p[1]))
+            except ValueError:
+                continue
+            for nm, val in zip(names, p[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------
+# inputs
+# ---------------------------------------------------------------------------------------
+def host_inputs(name, rank, world):
+    """Seeded host tensors of this rank's shard (generated whole, then cut, so that every
+    world size sees the same configuration)."""
+    from custom_matmul_kernels_b200.sharding import shard_range
+    l, m, k, n = SHAPES[name]
+    g = torch.Generator().manual_seed(SEEDS[name])
+    out = {}
+    if name in ("c2", "c3"):
+        b0, b1 = shard_range(l, world, rank)
+        if name == "c2":
+            A = torch.rand(l, m, k, generator=g) * 2 - 1
+            B = torch.rand(l, k, n, generator=g) * 2 - 1
+        else:
+            A = torch.randn(l, m, k, generator=g)
+            B = torch.randn(l, k, n, generator=g)
+            half = l // 2
+            mask = torch.zeros(l, m, n, dtype=torch.bool)
+            mask[:half] = torch.tril(torch.ones(m, n, dtype=torch.bool))
+            tiles = torch.rand(l - half, m // 64, n // 64, generator=g) < 0.3
+            mask[half:] = tiles.repeat_interleave(64, 1).repeat_interleave(64, 2)
+            out["mask"] = mask[b0:b1].contiguous()
+        out["A"], out["B"] = A[b0:b1].contiguous(), B[b0:b1].contiguous()
+        out["units"] = b1 - b0
+        return out
+    if name in ("c1", "c4"):
+        r0, r1 = shard_range(m, world, rank, 128)
+        A = torch.randn(l, m, k, generator=g)
+        B = torch.randn(l, k, n, generator=g)
+        out["A"], out["B"] = A[:, r0:r1].contiguous(), B
+        out["units"] = r1 - r0
+        return out
+    # c5: columns of B sharded; generate per 64Ki-row / 64Ki-column pieces to bound host memory
+    c0, c1 = shard_range(n, world, rank, 128)
+    A = torch.randn(l, m, k, generator=g)
+    B = torch.empty(l, k, c1 - c0)
+    piece = 65536
+    for p0 in range(0, n, piece):  # B is generated column-piece by column-piece, every rank alike
+        blk = torch.randn(l, k, min(piece, n - p0), generator=g)
+        lo, hi = max(p0, c0), min(p0 + blk.shape[2], c1)
+        if lo < hi:
+            B[:, :, lo - c0:hi - c0] = blk[:, :, lo - p0:hi - p0]
+    out["A"], out["B"], out["col0"] = A, B, c0
+    out["units"] = m
+    return out
+
+
+# ---------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------
+class Workload:
+    def __init__(self, name, rank, world, dev):
+        from custom_matmul_kernels_b200 import BMMCUDA, MBMMCUDA, MinBMMCUDA, TopkBMMCUDA, make_masks
+        from custom_matmul_kernels_b200 import sharding
+        self.name, self.rank, self.world, self.dev = name, rank, world, dev
+        self.sharding = sharding
+        h = host_inputs(name, rank, world)
+        self.h = h
+        self.A_pin = h["A"].pin_memory()
+        self.B_pin = h["B"].pin_memory()
+        self.A = self.A_pin.to(dev)
+        self.B = self.B_pin.to(dev)
+        self.in_bytes = self.A.numel() * 4 + self.B.numel() * 4
+        self.kernels_per_step = 1
+        if name == "c3":
+            self.masks = make_masks(h["mask"].to(dev))
+            self.masks_pin = tuple(t.cpu().pin_memory() for t in self.masks)
+            self.in_bytes += sum(t.numel() for t in self.masks)
+            self.op = MBMMCUDA()
+        elif name == "c2":
+            self.op = BMMCUDA()
+        elif name in ("c1", "c4"):
+            self.op = MinBMMCUDA()
+            self.kernels_per_step = 2   # fused GEMM+min kernel, key-unpack kernel
+        else:
+            self.op = TopkBMMCUDA()
+            self.kernels_per_step = 1 + (1 if world > 1 else 0)  # + candidate merge
+        self.out_host = None
+
+    def run(self, A, B, masks=None):
+        n = self.name
+        if n == "c2":
+            return (self.op(A, B),)
+        if n == "c3":
+            return (self.op(A, B, *(masks or self.masks)),)
+        if n in ("c1", "c4"):
+            return self.op(A, B, dim=2)
+        return self.sharding.topk_bmm_column_sharded(
+            A, B, self.h["col0"], TOPK, lambda a, b, k, off: self.op(a, b, k=k, dim=2, index_offset=off))
+
+    def step(self):
+        return self.run(self.A, self.B)
+
+    def e2e_step(self):
+        self.A.copy_(self.A_pin, non_blocking=True)
+        self.B.copy_(self.B_pin, non_blocking=True)
+        masks = None
+        if self.name == "c3":
+            masks = self.masks
+            for d, s in zip(self.masks, self.masks_pin):
+                d.copy_(s, non_blocking=True)
+        outs = self.run(self.A, self.B, masks)
+        if self.out_host is None:
+            self.out_host = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in outs]
+        for hbuf, o in zip(self.out_host, outs):
+            hbuf.copy_(o, non_blocking=True)
+        return outs
+
+    def out_bytes(self):
+        return sum(h.numel() * h.element_size() for h in (self.out_host or []))
+
+
+def timed_steps(fn, steps, flush):
+    """K steps, each bracketed by CUDA events on the current stream; an L2 flush (outside
+    the events) between steps when the inputs fit in L2. Returns per-step ms."""
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for s in range(steps):
+        if flush is not None:
+            flush.add_(1.0)
+        ev[s][0].record()
+        fn()
+        ev[s][1].record()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in ev]
+
+
+def measure_tf32_cublas():
+    """cuBLAS TF32 throughput (fp32 torch.matmul with TF32 allowed, 8192^3, best of 10)."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        a = torch.randn(8192, 8192, device="cuda")
+        b = torch.randn(8192, 8192, device="cuda")
+        best = float("inf")
+        for i in range(13):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch.matmul(a, b)
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                best = min(best, e0.elapsed_time(e1))
+        return 2 * 8192 ** 3 / best / 1e9
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16": p["bf16_tflops"], "bf16_sustained": p["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
+
+
+def algorithmic_bytes(name, units):
+    """Compulsory HBM bytes of one launch over `units` rows/batches of this rank."""
+    l, m, k, n = SHAPES[name]
+    if name == "c2":
+        return units * (m * k + k * n + m * n) * 4
+    if name == "c3":
+        return units * ((m * k + k * n + m * n) * 4 + (m // 128) * (n // 128) + (m // 8) * (n // 8))
+    if name in ("c1", "c4"):
+        return units * k * 4 + k * n * 4 + units * 12
+    return units * k * 4 + k * n * 4 + units * TOPK * 12
+
+
+def cpu_baseline(name):
+    """Reference semantics on the host cores over a bounded sample (rank 0, N=1)."""
+    from oracle import ref_semantics as R
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    l, m, k, n = SHAPES[name]
+    t_budget = 10.0
+    if name in ("c1", "c4"):
+        rows = 8192 if name == "c4" else 16384
+        d = R.make_inputs(name, rows=rows)
+        fn = lambda: torch.bmm(d["A"], d["B"]).min(dim=-1)  # noqa: E731
+        fn()
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < t_budget:
+            fn()
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        return {"value": rows / dt, "unit": "rows/s", "cores": cores, "kind": "port",
+                "sample": f"{rows} rows x all {n} columns, torch.bmm + min on CPU, mean of {reps} passes"}
+    if name == "c5":
+        rows = 256
+        d = R.make_inputs("c5", rows=rows, cols=n)
+        t0 = time.perf_counter()
+        R.cpu_topk_bmm_chunked(d["A"], d["B"], TOPK)
+        dt = time.perf_counter() - t0
+        return {"value": rows / dt, "unit": "rows/s", "cores": cores, "kind": "port",
+                "sample": f"{rows} rows x all {n} columns in 131072-column chunks with a running top-64, one pass"}
+    batches = 8
+    d = R.make_inputs(name, batches=batches)
+    if name == "c2":
+        fn = lambda: torch.bmm(d["A"], d["B"])  # noqa: E731
+    else:
+        fn = lambda: torch.bmm(d["A"], d["B"]).masked_fill_(~d["mask"], 0)  # noqa: E731
+    fn()
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < t_budget:
+        fn()
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": batches / dt, "unit": "batches/s", "cores": cores, "kind": "port",
+            "sample": f"{batches} of {l} batches, torch.bmm{' + masked_fill' if name == 'c3' else ''} on CPU, mean of {reps} passes"}
+
+
+UNIT = {"c1": "rows/s", "c2": "batches/s", "c3": "batches/s", "c4": "rows/s", "c5": "rows/s"}
+
+
+def config_dict(name, world, flush):
+    l, m, k, n = SHAPES[name]
+    part = {"c1": "A rows", "c4": "A rows", "c2": "batches", "c3": "batches", "c5": "B columns + all-gather"}[name]
+    return {"workload": f"{name}: {OPS[name]} A[{l},{m},{k}] B[{l},{k},{n}]" + (f" k={TOPK}" if name == "c5" else ""),
+            "sharding": f"{part} over {world} GPU(s)", "precision": "fp32 in/out, 3xTF32 tensor-core products",
+            "l2": "flushed between steps" if flush else "inputs exceed L2"}
+
+
+def run_ours(args):
+    rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    name = args.workload
+    wl = Workload(name, rank, world, dev)
+    flush = None
+    if wl.in_bytes < 2 * L2_BYTES:
+        flush = torch.zeros(L2_BYTES * 2 // 4, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        wl.step()
+    barrier()
+    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                           os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    if rank == 0:
+        sampler.start()
+    ms = timed_steps(wl.step, args.steps, flush)
+    barrier()
+    # end to end: pinned host -> device -> op -> pinned host, every step
+    for _ in range(2):
+        wl.e2e_step()
+    barrier()
+    ms_e2e = timed_steps(wl.e2e_step, args.steps, None)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+
+    tot = torch.tensor([sum(ms), sum(ms_e2e)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(tot, op=dist.ReduceOp.MAX)
+    total_ms, total_e2e_ms = float(tot[0]), float(tot[1])
+    l, m, k, n = SHAPES[name]
+    units_total = l if name in ("c2", "c3") else m
+    if rank == 0:
+        ms_per_step = total_ms / args.steps
+        value = units_total / (ms_per_step / 1e3)
+        peaks = load_peaks()
+        # dominant kernel of this rank: the fused GEMM; the step's other kernels (key
+        # unpack, candidate merge) are a few microseconds and ride inside the same events
+        launch_ms = statistics.mean(ms)
+        flops_launch = 2.0 * (wl.h["units"] if name not in ("c2", "c3") else wl.h["units"] * m) * n * k
+        if name == "c5":
+            flops_launch = 2.0 * m * wl.B.shape[2] * k
+        bytes_launch = algorithmic_bytes(name, wl.h["units"]) if name != "c5" else (
+            m * k * 4 + k * wl.B.shape[2] * 4 + m * TOPK * 12)
+        tensor_time = flops_launch * 3 / ((peaks["bf16"] / 2) * 1e12)
+        hbm_time = bytes_launch / (peaks["hbm_gbs"] * 1e9)
+        if hbm_time > tensor_time:
+            roof = {"bound": "hbm", "achieved": bytes_launch / (launch_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"],
+                    "unit": "GB/s"}
+        else:
+            sustained = total_ms > 500.0
+            peak = (peaks["bf16_sustained"] if sustained else peaks["bf16"]) / 2 / 3
+            roof = {"bound": "tensor", "achieved": flops_launch / (launch_ms / 1e3) / 1e12, "peak": peak,
+                    "unit": "TFLOP/s",
+                    "peak_note": f"{peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} / 2 (tf32) / 3 "
+                                 "(three tf32 MMAs per fp32 product)"}
+        roof["frac"] = roof["achieved"] / roof["peak"]
+        roof["traffic"] = None
+        roof["kernel"] = "fbmm_gemm_kernel"
+        if world == 1:
+            roof["tf32_cublas_tflops_live"] = measure_tf32_cublas()
+        line = {
+            "metric": f"fused {OPS[name]} throughput ({name})", "value": value, "unit": UNIT[name], "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_dict(name, world, flush is not None),
+            "tflops": 2.0 * l * m * n * k / (ms_per_step / 1e3) / 1e12,
+            "e2e": {"value": units_total / (total_e2e_ms / args.steps / 1e3), "unit": UNIT[name],
+                    "h2d_bytes_per_step": wl.in_bytes, "d2h_bytes_per_step": wl.out_bytes(),
+                    "note": "bytes are this rank's; every rank copies its own shard"},
+            "gpu_launches": wl.kernels_per_step * args.steps * world,
+            "clocks": clocks, "roofline": roof,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(name)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------
+# reference arm: the reference's semantics on the host cores
+# ---------------------------------------------------------------------------------------
+def run_reference(args):
+    rank, world = env_int("RANK", 0), env_int("WORLD_SIZE", 1)
+    if rank != 0:
+        return
+    from oracle import ref_semantics as R
+    name = args.workload
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    l, m, k, n = SHAPES[name]
+    if name in ("c1", "c4"):
+        rows = 8192 if name == "c4" else 16384
+        d = R.make_inputs(name, rows=rows)
+        step = lambda: torch.bmm(d["A"], d["B"]).min(dim=-1)  # noqa: E731
+        units, sample = rows, f"{rows} rows x all {n} columns per step"
+    elif name == "c5":
+        rows = 128
+        d = R.make_inputs("c5", rows=rows, cols=n)
+        step = lambda: R.cpu_topk_bmm_chunked(d["A"], d["B"], TOPK)  # noqa: E731
+        units, sample = rows, f"{rows} rows x all {n} columns per step, running top-64 over 131072-column chunks"
+    else:
+        batches = 8
+        d = R.make_inputs(name, batches=batches)
+        if name == "c2":
+            step = lambda: torch.bmm(d["A"], d["B"])  # noqa: E731
+        else:
+            step = lambda: torch.bmm(d["A"], d["B"]).masked_fill_(~d["mask"], 0)  # noqa: E731
+        units, sample = batches, f"{batches} of {l} batches per step"
+    for _ in range(max(args.warmup, 1)):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = units / dt
+    line = {
+        "impl": "reference", "metric": f"fused {OPS[name]} throughput ({name})", "value": value, "unit": UNIT[name],
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(name, world, False),
+        "cpu_baseline": {"value": value, "unit": UNIT[name], "cores": cores, "kind": "port",
+                         "sample": sample + "; torch CPU restatement of the reference's test expressions "
+                                            "(the reference's kernels need CuPy and a GPU)"},
+        "e2e": {"value": value, "unit": UNIT[name], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c4", choices=sorted(SHAPES))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.steps is None:
+        args.steps = {"c1": 50, "c2": 30, "c3": 30, "c4": 10, "c5": 2}[args.workload]
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -197,24 +197,34 @@ int make_row_problem(RowProblem* p, const float* A, int a_layout, long long lda,
 }
 
 // Column chunking: with few row blocks, split the column sweep so that every SM has
-// work. Picks the chunk count with the smallest modelled makespan; `overhead_tiles` is
-// the cost of one extra unit in tile-times.
+// work. Models the makespan of each chunk count (`overhead_tiles` is the cost of one
+// extra unit in tile-times) and takes the SMALLEST count within 5% of the best: extra
+// chunks cost scratch memory and merge work, so they must pay for themselves.
 void choose_chunks(int L, int m_blocks, int n_tiles, int sms, int overhead_tiles, int max_chunks, int* n_chunks,
                    int* tiles_per_chunk) {
   const long long base = static_cast<long long>(L) * m_blocks;
-  long long best_cost = -1;
-  int best_c = 1, best_tpc = n_tiles;
   const int limit = n_tiles < max_chunks ? n_tiles : max_chunks;
-  for (int c = 1; c <= limit; ++c) {
+  auto cost_of = [&](int c, int* cc_out, int* tpc_out) -> long long {
     const int tpc = (n_tiles + c - 1) / c;
     const int cc = (n_tiles + tpc - 1) / tpc;
     const long long units = base * cc;
     const long long waves = (units + sms - 1) / sms;
-    const long long cost = waves * (tpc + overhead_tiles);
-    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_c = cc; best_tpc = tpc; }
+    *cc_out = cc;
+    *tpc_out = tpc;
+    return waves * (tpc + overhead_tiles);
+  };
+  long long best_cost = -1;
+  int cc, tpc;
+  for (int c = 1; c <= limit; ++c) {
+    const long long cost = cost_of(c, &cc, &tpc);
+    if (best_cost < 0 || cost < best_cost) best_cost = cost;
   }
-  *n_chunks = best_c;
-  *tiles_per_chunk = best_tpc;
+  for (int c = 1; c <= limit; ++c) {
+    const long long cost = cost_of(c, &cc, &tpc);
+    if (cost * 100 <= best_cost * 105) break;
+  }
+  *n_chunks = cc;
+  *tiles_per_chunk = tpc;
 }
 
 constexpr int kMinOverheadTiles = 1;

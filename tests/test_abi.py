@@ -1,0 +1,130 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports every symbol the header
+declares, validates arguments before touching a device, and answers workspace queries."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+from custom_matmul_kernels_b200 import custom_kernel as ck
+
+HEADER = os.path.join(ROOT, "include", "fbmm.h")
+
+
+def declared_symbols():
+    text = open(HEADER).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(fbmm_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_exported(lib):
+    syms = declared_symbols()
+    assert len(syms) >= 10
+    for s in syms:
+        assert hasattr(lib, s), f"{s} declared in include/fbmm.h but not exported"
+        assert s in ck.SIGNATURES, f"{s} has no ctypes signature"
+    assert sorted(ck.SIGNATURES) == syms
+
+
+def test_header_cites_reference_for_every_entry_point():
+    text = open(HEADER).read()
+    for cite in ("kernels/bmm.cu:185", "kernels/mbmm.cu:209", "kernels/minbmm.cu:348", "kernels/topkbmm.cu:500",
+                 "kernels/bitonic_sort.cu:183", "custom_kernel.py:12"):
+        assert cite in text
+
+
+def test_version_and_error_string(lib):
+    assert lib.fbmm_version() >= 1000
+    assert isinstance(lib.fbmm_last_error(), bytes)
+
+
+def _call_bmm(lib, A=64, lda=4, B=64, ldb=4, C=64, l=1, m=4, n=4, k=4, la=ord("n"), lb=ord("n")):
+    return lib.fbmm_bmm_f32(None, A, la, lda, m * k, B, lb, ldb, k * n, C, n, m * n, l, m, n, k)
+
+
+def test_argument_validation_needs_no_device(lib):
+    # every one of these returns before any CUDA call
+    assert _call_bmm(lib, m=0) == ck.FBMM_ERR_INVALID
+    assert b"positive" in lib.fbmm_last_error()
+    assert _call_bmm(lib, C=None) == ck.FBMM_ERR_INVALID
+    assert _call_bmm(lib, la=ord("x")) == ck.FBMM_ERR_INVALID
+    assert _call_bmm(lib, A=None) == ck.FBMM_ERR_INVALID
+    assert _call_bmm(lib, A=68) == ck.FBMM_ERR_ALIGN          # base not 16-byte aligned
+    assert _call_bmm(lib, lda=6, k=6, ldb=4) == ck.FBMM_ERR_ALIGN   # pitch not a multiple of 4
+    assert _call_bmm(lib, lda=2) == ck.FBMM_ERR_INVALID       # pitch shorter than a row
+    with pytest.raises(ValueError):
+        ck.check(_call_bmm(lib, m=-1))
+
+
+def test_topk_and_min_validation(lib):
+    rc = lib.fbmm_topk_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 129, 2, 0, None, 0)
+    assert rc == ck.FBMM_ERR_INVALID and b"1..128" in lib.fbmm_last_error()
+    rc = lib.fbmm_topk_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 8, 3, 0, None, 0)
+    assert rc == ck.FBMM_ERR_INVALID and b"dim" in lib.fbmm_last_error()
+    rc = lib.fbmm_min_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 2, None, 0)
+    assert rc == ck.FBMM_ERR_WORKSPACE
+    rc = lib.fbmm_topk_merge_f32(None, 64, 64, 0, 4, 8, 64, 64)
+    assert rc == ck.FBMM_ERR_INVALID
+
+
+def test_workspace_queries(lib):
+    assert lib.fbmm_min_bmm_workspace_bytes(1, 16384, 16384, 64, 2) == 16384 * 8
+    assert lib.fbmm_min_bmm_workspace_bytes(2, 100, 300, 64, 1) == 2 * 300 * 8
+    # many row blocks: one column chunk, lists live in the outputs, no scratch
+    assert lib.fbmm_topk_bmm_workspace_bytes(1, 1 << 20, 1 << 20, 256, 64, 2) == 0
+    # few row blocks: per-chunk candidate lists
+    assert lib.fbmm_topk_bmm_workspace_bytes(1, 128, 1 << 16, 64, 64, 2) > 0
+
+
+def test_wrappers_reject_bad_inputs_on_cpu():
+    from custom_matmul_kernels_b200 import BMMCUDA, MBMMCUDA, MinBMMCUDA, TopkBMMCUDA
+    A, B = torch.zeros(2, 4, 8), torch.zeros(2, 8, 4)
+    for op in (BMMCUDA(), MinBMMCUDA(), TopkBMMCUDA()):
+        with pytest.raises(ValueError):
+            op(A, B)  # not CUDA tensors
+        with pytest.raises(ValueError):
+            op(A, torch.zeros(2, 7, 4))
+        with pytest.raises(TypeError):
+            op(A.half(), B.half())
+        with pytest.raises(ValueError):
+            op(A[0], B)
+    with pytest.raises(NotImplementedError):
+        MinBMMCUDA(distance="l2")
+    with pytest.raises(ValueError):
+        TopkBMMCUDA(distance="cosine")
+    assert BMMCUDA().get_mode(A, B.transpose(1, 2).contiguous().transpose(1, 2)) == "nt"
+    assert MBMMCUDA(share_mask=True).share_mask is True
+
+
+def test_operand_descriptor_logic():
+    """`operand` passes TMA-addressable storage through and repacks the rest."""
+    X = torch.zeros(2, 8, 12)
+    keep, t, ld, bs = ck.operand(X)
+    assert keep is X and not t and ld == 12 and bs == 96
+    Xt = torch.zeros(2, 12, 8).transpose(1, 2)          # stored [l][12][8], logical [l][8][12]
+    keep, t, ld, bs = ck.operand(Xt)
+    assert keep is Xt and t and ld == 8
+    odd = torch.arange(2 * 5 * 7, dtype=torch.float32).view(2, 5, 7)   # pitch 7: not addressable
+    keep, t, ld, bs = ck.operand(odd)
+    assert keep is not odd and not t and ld == 8 and bs == 40
+    assert torch.equal(keep[:, :, :7], odd) and bool((keep[:, :, 7:] == 0).all())
+    off = torch.zeros(2 * 8 * 12 + 1)[1:].view(2, 8, 12)               # base off by 4 bytes
+    keep, _, _, _ = ck.operand(off)
+    assert keep.data_ptr() % 16 == 0
+    bc = torch.zeros(1, 8, 12).expand(3, 8, 12)                        # broadcast batch
+    keep, _, _, bs = ck.operand(bc)
+    assert bs == 96
+
+
+def test_make_masks_matches_oracle():
+    from custom_matmul_kernels_b200 import make_masks
+    from oracle import ref_semantics as R
+    g = torch.Generator().manual_seed(1)
+    mask = torch.rand(2, 200, 136, generator=g) < 0.2
+    mask[0, :128, :128] = False
+    for a, b in zip(make_masks(mask), R.make_masks(mask)):
+        assert torch.equal(a, b)
+    for a, b in zip(make_masks(mask[0]), R.make_masks(mask[0])):
+        assert torch.equal(a, b)

@@ -1,0 +1,98 @@
+"""CPU tests of the multi-GPU partition / exchange logic: two gloo ranks, oracle compute."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from custom_matmul_kernels_b200 import sharding as S
+from oracle import ref_semantics as R
+
+
+def test_shard_range_covers_everything_once():
+    for total, world, gran in [(1048576, 8, 128), (1000, 3, 128), (5, 8, 1), (128, 2, 128), (0, 2, 1)]:
+        seen = []
+        for r in range(world):
+            b, e = S.shard_range(total, world, r, gran)
+            assert 0 <= b <= e <= total
+            if b < e:
+                assert b % gran == 0
+            seen += list(range(b, e))
+        assert seen == list(range(total))
+    with pytest.raises(ValueError):
+        S.shard_range(10, 2, 2)
+
+
+def test_merge_candidates_torch_handles_empty_slots():
+    v = torch.tensor([[[5., 3., float("-inf")]], [[4., 4., 1.]]])
+    i = torch.tensor([[[7, 2, -1]], [[9, 11, 30]]])
+    mv, mi = S.merge_candidates_torch(v, i, 3)
+    assert mv.tolist() == [[5., 4., 4.]] and sorted(mi[0].tolist()) == [7, 9, 11]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(7)
+        A = torch.randn(1, 300, 24, generator=g)
+        B = torch.randn(1, 24, 1000, generator=g)
+        k = 9
+
+        def local_topk(a, b, kk, off):
+            v, i = R.topk_bmm(a, b, k=kk, dim=2)
+            return v, torch.where(i >= 0, i + off, i)
+
+        # column shards + one all-gather + merge
+        B_loc, off = S.column_shard(B)
+        v, i = S.topk_bmm_column_sharded(A, B_loc.contiguous(), off, k, local_topk, merge=S.merge_candidates_torch)
+        R.check_topk(v, i, A, B, k, 2)
+        wv, _ = R.topk_bmm(A, B, k=k, dim=2)
+        assert torch.equal(v, wv)
+
+        # row shards: no communication, concatenation of rank outputs is the full answer
+        A_loc, r0 = S.row_shard(A)
+        mv, mi = R.min_bmm(A_loc, B, dim=2)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (r0, mv, mi))
+        full_v = torch.cat([x[1] for x in sorted(gathered, key=lambda x: x[0])], dim=1)
+        full_i = torch.cat([x[2] for x in sorted(gathered, key=lambda x: x[0])], dim=1)
+        ov, oi = R.min_bmm(A, B, dim=2)
+        assert torch.equal(full_v, ov) and torch.equal(full_i, oi)
+
+        # batch shards
+        Ab = torch.randn(5, 8, 4, generator=g)
+        sl = S.batch_shard(Ab)
+        counts = [None] * world
+        dist.all_gather_object(counts, sl.shape[0])
+        assert sum(counts) == 5
+        if rank == 0:
+            out.put("ok")
+    except Exception as e:  # surface the failure to the parent
+        if rank == 0:
+            out.put(f"fail: {e!r}")
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gloo_partitions_match_single_device():
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert out.get() == "ok"
