@@ -360,11 +360,14 @@ def run_ours(args):
     ms = timed_steps(wl.step, args.steps, flush)
     barrier()
     # end to end: pinned host -> device -> op -> pinned host, every step
-    for _ in range(2):
-        wl.e2e_step()
-    barrier()
-    ms_e2e = timed_steps(wl.e2e_step, args.steps, None)
-    barrier()
+    if args.no_e2e:
+        ms_e2e = [float("nan")] * args.steps
+    else:
+        for _ in range(2):
+            wl.e2e_step()
+        barrier()
+        ms_e2e = timed_steps(wl.e2e_step, args.steps, None)
+        barrier()
     clocks = sampler.stop() if rank == 0 else None
 
     tot = torch.tensor([sum(ms), sum(ms_e2e)], device=dev, dtype=torch.float64)
@@ -414,6 +417,8 @@ def run_ours(args):
             "gpu_launches": wl.kernels_per_step * args.steps * world,
             "clocks": clocks, "roofline": roof,
         }
+        if args.rows is not None or args.batches is not None:
+            line["reduced"] = True
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(name)
         print(json.dumps(line), flush=True)
@@ -479,9 +484,20 @@ def main():
     ap.add_argument("--workload", default="c4", choices=sorted(SHAPES))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--rows", type=int, default=None,
+                    help="profiling only: cut c1/c4/c5 to this many rows of A (the line is marked reduced)")
+    ap.add_argument("--batches", type=int, default=None,
+                    help="profiling only: cut c2/c3 to this many batches (the line is marked reduced)")
+    ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the end-to-end leg")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = {"c1": 50, "c2": 30, "c3": 30, "c4": 10, "c5": 2}[args.workload]
+    if args.rows is not None and args.workload in ("c1", "c4", "c5"):
+        l, m, k, n = SHAPES[args.workload]
+        SHAPES[args.workload] = (l, args.rows, k, n)
+    if args.batches is not None and args.workload in ("c2", "c3"):
+        l, m, k, n = SHAPES[args.workload]
+        SHAPES[args.workload] = (args.batches, m, k, n)
     if args.impl == "reference":
         run_reference(args)
     else:

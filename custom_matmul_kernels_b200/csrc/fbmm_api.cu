@@ -47,14 +47,12 @@ std::mutex g_mu;
 DeviceState g_dev[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
 
-constexpr int kStages = 3;
-constexpr int kTileN = 128;
-
 template <int EPI, int E>
 int set_smem_attr() {
-  using Traits = KernelTraits<kTileN, kStages, EPI, E>;
-  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<kTileN, kStages, EPI, E>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Traits::kSmemBytes)));
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kSmemLimit)));
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kSmemLimit)));
   return FBMM_OK;
 }
 
@@ -227,20 +225,27 @@ void choose_chunks(int L, int m_blocks, int n_tiles, int sms, int overhead_tiles
   *tiles_per_chunk = tpc;
 }
 
+constexpr int kStoreOverheadTiles = 1;
 constexpr int kMinOverheadTiles = 1;
 constexpr int kTopkOverheadTiles = 12;
 constexpr int kMaxChunks = 64;
 
 template <int EPI, int E>
 int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p, GemmShape shape, const EpiArgs& epi) {
-  using Traits = KernelTraits<kTileN, kStages, EPI, E>;
   CUtensorMap ta, tb;
   int rc;
   if ((rc = make_tensor_map(&ta, p.a, p.K, p.L, kTileM)) != FBMM_OK) return rc;
   if ((rc = make_tensor_map(&tb, p.b, p.K, p.L, kTileN)) != FBMM_OK) return rc;
   const long long grid = shape.num_units < st.sms ? shape.num_units : st.sms;
-  fbmm_gemm_kernel<kTileN, kStages, EPI, E>
-      <<<static_cast<unsigned>(grid), kNumThreads, Traits::kSmemBytes, stream>>>(ta, tb, shape, epi);
+  const int kblocks = (p.K + kKBlock - 1) / kKBlock;
+  // Up to K = 128 the row block of A stays in shared memory for the whole unit.
+  const bool a_resident = kblocks <= kMaxResidentKBlocks;
+  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk);
+  if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
+  if (a_resident)
+    fbmm_gemm_kernel<EPI, E, true><<<static_cast<unsigned>(grid), kNumThreads, plan.total, stream>>>(ta, tb, shape, epi);
+  else
+    fbmm_gemm_kernel<EPI, E, false><<<static_cast<unsigned>(grid), kNumThreads, plan.total, stream>>>(ta, tb, shape, epi);
   FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
 }
@@ -265,6 +270,15 @@ size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 extern "C" {
 
 int fbmm_version(void) { return 1000; }
+
+#ifdef FBMM_PROFILE
+// Tuning builds only: copies the per-role wait counters of CTA 0 to `out` (16 values).
+int fbmm_debug_read_profile(long long* out) {
+  FBMM_CUDA(cudaDeviceSynchronize());
+  FBMM_CUDA(cudaMemcpyFromSymbol(out, fbmm::g_fbmm_prof, 16 * sizeof(long long)));
+  return FBMM_OK;
+}
+#endif
 
 const char* fbmm_last_error(void) { return g_err; }
 
@@ -294,8 +308,7 @@ int fbmm_bmm_f32(void* stream, const float* A, int a_layout, long long lda, long
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  s.n_chunks = s.n_tiles;
-  s.tiles_per_chunk = 1;
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   EpiArgs e{};
   e.C = C; e.ldc = ldc; e.stride_c = stride_c;
@@ -319,8 +332,7 @@ int fbmm_mbmm_f32(void* stream, const float* A, int a_layout, long long lda, lon
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  s.n_chunks = s.n_tiles;
-  s.tiles_per_chunk = 1;
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   EpiArgs e{};
   e.C = C; e.ldc = ldc; e.stride_c = stride_c;

@@ -5,7 +5,9 @@
 // kernels/minbmm.cu:348, kernels/topkbmm.cu:500 and their layout variants) with one
 // persistent, warp-specialised kernel:
 //
-//   warp 0      TMA producer: raw fp32 operand tiles -> shared-memory ring
+//   warp 0      TMA producer: raw fp32 operand tiles -> shared-memory ring (for K <= 128 the
+//               128 x K block of A is loaded once per unit and stays resident while the
+//               unit's column tiles stream past)
 //   warps 2-5   splitters: lo = x - tf32(x), written beside the raw tile (the raw tile
 //               itself serves as the hi plane because the tensor core ignores the low
 //               13 mantissa bits of a tf32 operand)
@@ -38,6 +40,23 @@ enum EpilogueKind { kEpiStore = 0, kEpiMask = 1, kEpiMin = 2, kEpiTopk = 3 };
 // Device status word (bit 0: a bounded wait ran out).
 __device__ unsigned int g_fbmm_status[4];
 
+// Optional per-role wait-time counters (cycles), compiled in only for tuning builds.
+#ifdef FBMM_PROFILE
+__device__ long long g_fbmm_prof[16];
+#define FBMM_PROF_DECL long long prof_t0_ = 0, prof_acc_[4] = {0, 0, 0, 0}
+#define FBMM_PROF_BEGIN() prof_t0_ = clock64()
+#define FBMM_PROF_END(i) prof_acc_[i] += clock64() - prof_t0_
+#define FBMM_PROF_FLUSH(base)                                                           \
+  if (blockIdx.x == 0) {                                                                \
+    for (int q_ = 0; q_ < 4; ++q_) g_fbmm_prof[(base) + q_] = prof_acc_[q_];            \
+  }
+#else
+#define FBMM_PROF_DECL
+#define FBMM_PROF_BEGIN()
+#define FBMM_PROF_END(i)
+#define FBMM_PROF_FLUSH(base)
+#endif
+
 struct GemmShape {
   int L, M, N, K;
   int a_mn;  // A stored [l][k][m] (m contiguous) instead of [l][m][k]
@@ -66,18 +85,6 @@ struct EpiArgs {
   int k;
   long long index_offset;     // added to every column index written (column shards)
   long long topk_chunk_rows;  // rows between the lists of consecutive column chunks (0: one chunk)
-};
-
-template <int TILE_N>
-struct StageLayout {
-  static constexpr uint32_t kABytes = kTileM * kKBlock * 4;
-  static constexpr uint32_t kBBytes = TILE_N * kKBlock * 4;
-  static constexpr uint32_t kAHi = 0;
-  static constexpr uint32_t kALo = kABytes;
-  static constexpr uint32_t kBHi = 2 * kABytes;
-  static constexpr uint32_t kBLo = 2 * kABytes + kBBytes;
-  static constexpr uint32_t kBytes = 2 * kABytes + 2 * kBBytes;
-  static constexpr uint32_t kTxBytes = kABytes + kBBytes;
 };
 
 // Order-preserving map fp32 -> uint32 (smaller float <=> smaller key).
@@ -203,69 +210,119 @@ __device__ __noinline__ float topk_merge_rows(uint32_t need, uint32_t has_list, 
 // --------------------------------------------------------------------------------------
 // the kernel
 // --------------------------------------------------------------------------------------
-template <int TILE_N, int STAGES, int EPI, int TOPK_E>
-struct KernelTraits {
-  using Stage = StageLayout<TILE_N>;
-  static constexpr int kAccStages = 2;
-  static_assert(2 * kAccStages * TILE_N <= kTmemCols, "TMEM budget");
-  // top-k staging: kTopkStage slots per row, slot-major [slot][row]
-  static constexpr int kTopkStage = 32;
-  static constexpr uint32_t kEpiSmemBytes = (EPI == kEpiTopk) ? kTopkStage * kTileM * 8u : 0u;
-  static constexpr uint32_t kSmemBytes = STAGES * Stage::kBytes + kEpiSmemBytes + 1024u /*align*/ + 256u /*barriers*/;
-};
+// Shared-memory plan, computed identically on the host (launch size) and in the kernel.
+//   [A region: kblocks x (hi 16 KB | lo 16 KB)]      only when A stays resident
+//   [ring: stages x stage_bytes]                     stage = (A hi | A lo |) B hi | B lo
+//   [top-k staging] [barriers]
+constexpr int kTileN = 128;
+constexpr int kMaxStages = 8;
+constexpr int kMaxResidentKBlocks = 4;  // A stays resident up to K = 128
+constexpr uint32_t kPlaneBytes = kTileM * kKBlock * 4;  // one 128 x 32 fp32 plane: 16 KB
+constexpr uint32_t kTopkStageSlots = 32;                // staged candidates per row
+constexpr uint32_t kTopkStageBytes = kTopkStageSlots * kTileM * 8u;
+constexpr uint32_t kBarrierBytes = 512;
+constexpr uint32_t kSmemLimit = 232448;  // 227 KB per CTA on sm_100
 
-template <int TILE_N, int STAGES, int EPI, int TOPK_E>
+struct SmemPlan {
+  uint32_t a_bytes, stage_bytes, stages, epi_bytes, total;
+};
+__host__ __device__ inline SmemPlan make_smem_plan(bool a_resident, int kblocks, bool topk) {
+  SmemPlan p;
+  p.a_bytes = a_resident ? static_cast<uint32_t>(kblocks) * 2u * kPlaneBytes : 0u;
+  p.stage_bytes = a_resident ? 2u * kPlaneBytes : 4u * kPlaneBytes;
+  p.epi_bytes = topk ? kTopkStageBytes : 0u;
+  const uint32_t fixed = p.a_bytes + p.epi_bytes + kBarrierBytes + 1024u /* alignment slack */;
+  uint32_t st = (kSmemLimit - fixed) / p.stage_bytes;
+  p.stages = st > static_cast<uint32_t>(kMaxStages) ? static_cast<uint32_t>(kMaxStages) : st;
+  p.total = fixed + p.stages * p.stage_bytes;
+  return p;
+}
+
+struct Barriers {
+  uint64_t full[kMaxStages];    // TMA landed in ring stage
+  uint64_t split[kMaxStages];   // lo plane(s) of ring stage written
+  uint64_t empty[kMaxStages];   // MMAs done reading ring stage
+  uint64_t acc_full[2];         // accumulator stage complete
+  uint64_t acc_empty[2];        // accumulator stage drained by the epilogue
+  uint64_t a_full[kMaxResidentKBlocks];   // resident A k-block landed
+  uint64_t a_split[kMaxResidentKBlocks];  // its lo plane written
+  uint64_t a_empty[kMaxResidentKBlocks];  // last MMA of the unit done reading it
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+static_assert(sizeof(Barriers) <= kBarrierBytes, "barrier block too large");
+
+// lo plane of `bytes` bytes of fp32 at `hi`, written to `lo` (same layout), by the 128
+// splitter threads.
+__device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint32_t bytes, int st) {
+  const float4* src = reinterpret_cast<const float4*>(hi);
+  float4* dst = reinterpret_cast<float4*>(lo);
+#pragma unroll 8
+  for (int i = st; i < static_cast<int>(bytes / 16); i += kSplitThreads) {
+    const float4 x = src[i];
+    dst[i] = make_float4(split_lo(x.x), split_lo(x.y), split_lo(x.z), split_lo(x.w));
+  }
+}
+
+template <int EPI, int TOPK_E, bool A_RES>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmShape shape, const EpiArgs epi) {
-  using Traits = KernelTraits<TILE_N, STAGES, EPI, TOPK_E>;
-  using Stage = typename Traits::Stage;
-  constexpr int kAccStages = Traits::kAccStages;
+  constexpr int TILE_N = kTileN;
+  constexpr int kAccStages = 2;
+  static_assert(2 * kAccStages * TILE_N <= kTmemCols, "TMEM budget");
+
+  const int kblocks = (shape.K + kKBlock - 1) / kKBlock;
+  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk);
+  const uint32_t stages = plan.stages;
+  // offsets inside a ring stage
+  const uint32_t off_a_hi = 0, off_a_lo = kPlaneBytes;
+  const uint32_t off_b_hi = A_RES ? 0u : 2u * kPlaneBytes;
+  const uint32_t off_b_lo = off_b_hi + kPlaneBytes;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* stage_base = smem;
-  uint8_t* epi_smem = smem + STAGES * Stage::kBytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Traits::kEpiSmemBytes);
-  uint64_t* bar_full = bars;                      // TMA landed            [STAGES]
-  uint64_t* bar_split = bars + STAGES;            // lo planes written     [STAGES]
-  uint64_t* bar_empty = bars + 2 * STAGES;        // MMAs done with stage  [STAGES]
-  uint64_t* bar_acc_full = bars + 3 * STAGES;     // accumulators complete [kAccStages]
-  uint64_t* bar_acc_empty = bar_acc_full + kAccStages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_acc_empty + kAccStages);
-  volatile uint32_t* abort_flag = tmem_slot + 1;
+  uint8_t* a_region = smem;
+  uint8_t* ring = smem + plan.a_bytes;
+  uint8_t* epi_smem = ring + stages * plan.stage_bytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(epi_smem + plan.epi_bytes);
+  volatile uint32_t* abort_flag = &bars->abort_flag;
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
 
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&bar_full[s], 1);
-      mbar_init(&bar_split[s], kSplitThreads);
-      mbar_init(&bar_empty[s], 1);
+    bars->abort_flag = 0;
+    for (int s = 0; s < kMaxStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->split[s], kSplitThreads);
+      mbar_init(&bars->empty[s], 1);
     }
     for (int s = 0; s < kAccStages; ++s) {
-      mbar_init(&bar_acc_full[s], 1);
-      mbar_init(&bar_acc_empty[s], kEpiThreads);
+      mbar_init(&bars->acc_full[s], 1);
+      mbar_init(&bars->acc_empty[s], kEpiThreads);
+    }
+    for (int s = 0; s < kMaxResidentKBlocks; ++s) {
+      mbar_init(&bars->a_full[s], 1);
+      mbar_init(&bars->a_split[s], kSplitThreads);
+      mbar_init(&bars->a_empty[s], 1);
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_alloc(&bars->tmem_base, kTmemCols);
     tmem_relinquish_alloc_permit();
   }
   tcgen05_fence_before_sync();
   __syncthreads();
   tcgen05_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_base = bars->tmem_base;
 
-  const int kblocks = (shape.K + kKBlock - 1) / kKBlock;
   const long long units = shape.num_units;
 
-  // Decodes unit u; returns the tile range.
+  // Decodes unit u into batch, row block and column-tile range.
   auto decode = [&](long long u, int& b, int& mb, int& t0, int& t1) {
     const int c = static_cast<int>(u % shape.n_chunks);
     const long long r = u / shape.n_chunks;
@@ -280,42 +337,89 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (EPI != kEpiMask) return true;
     return epi.block_mask[b * epi.bm_stride + static_cast<long long>(mb) * epi.bm_cols + t] != 0;
   };
+  // Sweep order inside a unit: CTAs start at different column tiles so that they do not
+  // all ask L2 for the same B tile at the same moment.
+  auto tile_at = [&](int t0, int t1, int i) -> int {
+#ifdef FBMM_ROTATE
+    const int n = t1 - t0;
+    const int rot = static_cast<int>((static_cast<long long>(blockIdx.x) * n) / gridDim.x);
+    int r = i - t0 + rot;
+    if (r >= n) r -= n;
+    return t0 + r;
+#else
+    (void)t0; (void)t1;
+    return i;
+#endif
+  };
+  // First and last live tile of a unit; false when the unit has none.
+  auto live_range = [&](int b, int mb, int t0, int t1, int& first, int& last) -> bool {
+    if (EPI != kEpiMask) { first = t0; last = t1 - 1; return t0 < t1; }
+    first = -1; last = -1;
+    for (int t = t0; t < t1; ++t)
+      if (tile_live(b, mb, t)) { if (first < 0) first = t; last = t; }
+    return first >= 0;
+  };
+
+  auto load_a = [&](uint8_t* dst, uint64_t* bar, int kb, int mb, int b) {
+    if (!shape.a_mn) {
+      tma_load_3d(dst, &tmap_a, bar, kb * kKBlock, mb * kTileM, b);
+    } else {
+#pragma unroll
+      for (int c = 0; c < kTileM / 32; ++c)
+        tma_load_3d(dst + c * 4096, &tmap_a, bar, mb * kTileM + c * 32, kb * kKBlock, b);
+    }
+  };
+  auto load_b = [&](uint8_t* dst, uint64_t* bar, int kb, int t, int b) {
+    if (!shape.b_mn) {
+      tma_load_3d(dst, &tmap_b, bar, kb * kKBlock, t * TILE_N, b);
+    } else {
+#pragma unroll
+      for (int c = 0; c < TILE_N / 32; ++c)
+        tma_load_3d(dst + c * 4096, &tmap_b, bar, t * TILE_N + c * 32, kb * kKBlock, b);
+    }
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, a_phase = 0;
       bool ok = true;
+      FBMM_PROF_DECL;
+      const long long prof_start = clock64();
       for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        int b, mb, t0, t1;
+        int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
-        for (int t = t0; t < t1 && ok; ++t) {
+        if (!live_range(b, mb, t0, t1, first, last)) continue;
+        for (int ti = first; ti <= last && ok; ++ti) {
+          const int t = tile_at(t0, t1, ti);
           if (!tile_live(b, mb, t)) continue;
           for (int kb = 0; kb < kblocks; ++kb) {
-            ok = mbar_wait(&bar_empty[stage], phase ^ 1u, abort_flag);
+            if (A_RES && ti == first) {
+              // the row block's A k-block, loaded once per unit as soon as the previous
+              // unit's last tile has finished with that k-block
+              ok = mbar_wait(&bars->a_empty[kb], a_phase ^ 1u, abort_flag);
+              if (!ok) break;
+              mbar_arrive_expect_tx(&bars->a_full[kb], kPlaneBytes);
+              load_a(a_region + kb * 2 * kPlaneBytes, &bars->a_full[kb], kb, mb, b);
+            }
+            FBMM_PROF_BEGIN();
+            ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag);
+            FBMM_PROF_END(0);
             if (!ok) break;
-            uint8_t* sb = stage_base + stage * Stage::kBytes;
-            mbar_arrive_expect_tx(&bar_full[stage], Stage::kTxBytes);
-            if (!shape.a_mn) {
-              tma_load_3d(sb + Stage::kAHi, &tmap_a, &bar_full[stage], kb * kKBlock, mb * kTileM, b);
-            } else {
-#pragma unroll
-              for (int c = 0; c < kTileM / 32; ++c)
-                tma_load_3d(sb + Stage::kAHi + c * 4096, &tmap_a, &bar_full[stage], mb * kTileM + c * 32,
-                            kb * kKBlock, b);
-            }
-            if (!shape.b_mn) {
-              tma_load_3d(sb + Stage::kBHi, &tmap_b, &bar_full[stage], kb * kKBlock, t * TILE_N, b);
-            } else {
-#pragma unroll
-              for (int c = 0; c < TILE_N / 32; ++c)
-                tma_load_3d(sb + Stage::kBHi + c * 4096, &tmap_b, &bar_full[stage], t * TILE_N + c * 32,
-                            kb * kKBlock, b);
-            }
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            uint8_t* sb = ring + stage * plan.stage_bytes;
+            mbar_arrive_expect_tx(&bars->full[stage], A_RES ? kPlaneBytes : 2 * kPlaneBytes);
+            if (!A_RES) load_a(sb + off_a_hi, &bars->full[stage], kb, mb, b);
+            load_b(sb + off_b_hi, &bars->full[stage], kb, t, b);
+            if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
         }
+        a_phase ^= 1u;
       }
+#ifdef FBMM_PROFILE
+      prof_acc_[1] = clock64() - prof_start;
+#endif
+      (void)prof_start;
+      FBMM_PROF_FLUSH(0);
       if (!ok) {
         // Give copies already in flight a bounded time to land before the CTA leaves.
         const long long t0c = clock64();
@@ -325,7 +429,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // A ring stage holds the B hi plane directly followed by the B lo plane, so one MMA
+      // of width 2 * TILE_N over both computes hi*hi into the big accumulator and hi*lo
+      // into the small one next to it while reading A_hi once.
+      static_assert(2 * TILE_N <= 256, "the merged hi|lo MMA needs 2 * TILE_N <= 256");
       const uint32_t idesc = make_idesc_tf32(kTileM, TILE_N, shape.a_mn != 0, shape.b_mn != 0);
+      const uint32_t idesc_wide = make_idesc_tf32(kTileM, 2 * TILE_N, shape.a_mn != 0, shape.b_mn != 0);
       const uint32_t a_lbo = shape.a_mn ? 4096u : 16u, a_sbo = shape.a_mn ? 512u : 1024u;
       const uint32_t b_lbo = shape.b_mn ? 4096u : 16u, b_sbo = shape.b_mn ? 512u : 1024u;
       const uint32_t a_kstep = shape.a_mn ? 1024u : 32u, b_kstep = shape.b_mn ? 1024u : 32u;
@@ -334,77 +443,99 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       auto desc = [](uint32_t addr, uint32_t lbo, uint32_t sbo, uint64_t type) -> uint64_t {
         return (make_smem_desc_sw128(addr, lbo, sbo) & ~(7ull << 61)) | type;
       };
-      uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0;
+      uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, a_phase = 0;
       bool ok = true;
+      FBMM_PROF_DECL;
       for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
-        int b, mb, t0, t1;
+        int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
-        for (int t = t0; t < t1 && ok; ++t) {
+        if (!live_range(b, mb, t0, t1, first, last)) continue;
+        for (int ti = first; ti <= last && ok; ++ti) {
+          const int t = tile_at(t0, t1, ti);
           if (!tile_live(b, mb, t)) continue;
-          ok = mbar_wait(&bar_acc_empty[acc_stage], acc_phase ^ 1u, abort_flag);
+          FBMM_PROF_BEGIN();
+          ok = mbar_wait(&bars->acc_empty[acc_stage], acc_phase ^ 1u, abort_flag);
+          FBMM_PROF_END(0);
           if (!ok) break;
           tcgen05_fence_after_sync();
           const uint32_t acc_big = tmem_base + acc_stage * (2 * TILE_N);
           const uint32_t acc_small = acc_big + TILE_N;
           for (int kb = 0; kb < kblocks; ++kb) {
-            ok = mbar_wait(&bar_split[stage], phase, abort_flag);
+            if (A_RES && ti == first) {
+              ok = mbar_wait(&bars->a_split[kb], a_phase, abort_flag);
+              if (!ok) break;
+            }
+            FBMM_PROF_BEGIN();
+            ok = mbar_wait(&bars->split[stage], phase, abort_flag);
+            FBMM_PROF_END(1);
             if (!ok) break;
             tcgen05_fence_after_sync();
-            const uint32_t sb = smem_u32(stage_base + stage * Stage::kBytes);
+            FBMM_PROF_BEGIN();
+            const uint32_t sb = smem_u32(ring + stage * plan.stage_bytes);
+            const uint32_t sa = A_RES ? smem_u32(a_region + kb * 2 * kPlaneBytes) : sb;
 #pragma unroll
             for (int ks = 0; ks < kKBlock / 8; ++ks) {
-              const uint64_t a_hi = desc(sb + Stage::kAHi + ks * a_kstep, a_lbo, a_sbo, a_type);
-              const uint64_t a_lo = desc(sb + Stage::kALo + ks * a_kstep, a_lbo, a_sbo, a_type);
-              const uint64_t b_hi = desc(sb + Stage::kBHi + ks * b_kstep, b_lbo, b_sbo, b_type);
-              const uint64_t b_lo = desc(sb + Stage::kBLo + ks * b_kstep, b_lbo, b_sbo, b_type);
+              const uint64_t a_hi = desc(sa + off_a_hi + ks * a_kstep, a_lbo, a_sbo, a_type);
+              const uint64_t a_lo = desc(sa + off_a_lo + ks * a_kstep, a_lbo, a_sbo, a_type);
+              const uint64_t b_hi = desc(sb + off_b_hi + ks * b_kstep, b_lbo, b_sbo, b_type);
               const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
-              umma_tf32(acc_small, a_lo, b_hi, idesc, acc);
-              umma_tf32(acc_small, a_hi, b_lo, idesc, 1u);
-              umma_tf32(acc_big, a_hi, b_hi, idesc, acc);
+              umma_tf32(acc_big, a_hi, b_hi, idesc_wide, acc);  // [big | small] (+)= A_hi * [B_hi | B_lo]
+              umma_tf32(acc_small, a_lo, b_hi, idesc, 1u);      // small += A_lo * B_hi
             }
-            umma_commit(&bar_empty[stage]);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            umma_commit(&bars->empty[stage]);
+            if (A_RES && ti == last) umma_commit(&bars->a_empty[kb]);
+            FBMM_PROF_END(2);
+            if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
           if (!ok) break;
-          umma_commit(&bar_acc_full[acc_stage]);
+          umma_commit(&bars->acc_full[acc_stage]);
           if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
         }
+        a_phase ^= 1u;
       }
+      FBMM_PROF_FLUSH(4);
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ hi/lo splitters
     const int st = static_cast<int>(threadIdx.x) - 64;
-    uint32_t stage = 0, phase = 0;
+    uint32_t stage = 0, phase = 0, a_phase = 0;
     bool ok = true;
+    FBMM_PROF_DECL;
     for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
-      int b, mb, t0, t1;
+      int b, mb, t0, t1, first, last;
       decode(u, b, mb, t0, t1);
-      for (int t = t0; t < t1 && ok; ++t) {
+      if (!live_range(b, mb, t0, t1, first, last)) continue;
+      for (int ti = first; ti <= last && ok; ++ti) {
+        const int t = tile_at(t0, t1, ti);
         if (!tile_live(b, mb, t)) continue;
         for (int kb = 0; kb < kblocks; ++kb) {
-          ok = mbar_wait(&bar_full[stage], phase, abort_flag);
+          if (A_RES && ti == first) {
+            ok = mbar_wait(&bars->a_full[kb], a_phase, abort_flag);
+            if (!ok) break;
+            uint8_t* ab = a_region + kb * 2 * kPlaneBytes;
+            split_plane(ab + off_a_hi, ab + off_a_lo, kPlaneBytes, st);
+            fence_proxy_async_smem();
+            mbar_arrive(&bars->a_split[kb]);
+          }
+          FBMM_PROF_BEGIN();
+          ok = mbar_wait(&bars->full[stage], phase, abort_flag);
+          FBMM_PROF_END(0);
           if (!ok) break;
-          uint8_t* sb = stage_base + stage * Stage::kBytes;
-          const float4* a_hi = reinterpret_cast<const float4*>(sb + Stage::kAHi);
-          float4* a_lo = reinterpret_cast<float4*>(sb + Stage::kALo);
-#pragma unroll 4
-          for (int i = st; i < static_cast<int>(Stage::kABytes / 16); i += kSplitThreads) {
-            const float4 x = a_hi[i];
-            a_lo[i] = make_float4(split_lo(x.x), split_lo(x.y), split_lo(x.z), split_lo(x.w));
-          }
-          const float4* b_hi = reinterpret_cast<const float4*>(sb + Stage::kBHi);
-          float4* b_lo = reinterpret_cast<float4*>(sb + Stage::kBLo);
-#pragma unroll 4
-          for (int i = st; i < static_cast<int>(Stage::kBBytes / 16); i += kSplitThreads) {
-            const float4 x = b_hi[i];
-            b_lo[i] = make_float4(split_lo(x.x), split_lo(x.y), split_lo(x.z), split_lo(x.w));
-          }
+          FBMM_PROF_BEGIN();
+          uint8_t* sb = ring + stage * plan.stage_bytes;
+          if (!A_RES) split_plane(sb + off_a_hi, sb + off_a_lo, kPlaneBytes, st);
+          split_plane(sb + off_b_hi, sb + off_b_lo, kPlaneBytes, st);
+          FBMM_PROF_END(1);
+          FBMM_PROF_BEGIN();
           fence_proxy_async_smem();
-          mbar_arrive(&bar_split[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          mbar_arrive(&bars->split[stage]);
+          FBMM_PROF_END(2);
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
       }
+      a_phase ^= 1u;
     }
+    if (st == 0) { FBMM_PROF_FLUSH(8); }
   } else {
     // ------------------------------------------------------------------ epilogue
     const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read
@@ -412,10 +543,11 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t lane_base = (quarter * 32u) << 16;
     uint32_t acc_stage = 0, acc_phase = 0;
     bool ok = true;
+    FBMM_PROF_DECL;
 
     // top-k staging (slot-major): values then indices
     float* stg_v = reinterpret_cast<float*>(epi_smem);
-    int* stg_i = reinterpret_cast<int*>(epi_smem + Traits::kTopkStage * kTileM * 4);
+    int* stg_i = reinterpret_cast<int*>(epi_smem + kTopkStageSlots * kTileM * 4);
 
     for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
       int b, mb, t0, t1;
@@ -437,7 +569,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const float* stg_v_w = stg_v + quarter * 32;
       const int* stg_i_w = stg_i + quarter * 32;
 
-      for (int t = t0; t < t1 && ok; ++t) {
+      for (int ti = t0; ti < t1 && ok; ++ti) {
+        const int t = tile_at(t0, t1, ti);
         const int col_tile = t * TILE_N;
         if (!tile_live(b, mb, t)) {
           // masked-out tile: the product is defined as zero (mbmm.py:74 pre-zeroes C).
@@ -448,14 +581,17 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                              ((reinterpret_cast<uintptr_t>(epi.C) & 15) == 0);
             int c = col_tile;
             if (vec)
-              for (; c + 4 <= c_end; c += 4) *reinterpret_cast<float4*>(crow + c) = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (; c + 4 <= c_end; c += 4) __stcs(reinterpret_cast<float4*>(crow + c), make_float4(0.f, 0.f, 0.f, 0.f));
             for (; c < c_end; ++c) crow[c] = 0.f;
           }
           continue;
         }
-        ok = mbar_wait(&bar_acc_full[acc_stage], acc_phase, abort_flag);
+        FBMM_PROF_BEGIN();
+        ok = mbar_wait(&bars->acc_full[acc_stage], acc_phase, abort_flag);
+        FBMM_PROF_END(0);
         if (!ok) break;
         tcgen05_fence_after_sync();
+        FBMM_PROF_BEGIN();
         const uint32_t acc_big = tmem_base + acc_stage * (2 * TILE_N) + lane_base;
         const uint32_t acc_small = acc_big + TILE_N;
 #pragma unroll 1
@@ -467,7 +603,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (c == TILE_N / 32 - 1) {
             // both accumulators of this stage are now in registers: hand the stage back
             tcgen05_fence_before_sync();
-            mbar_arrive(&bar_acc_empty[acc_stage]);
+            mbar_arrive(&bars->acc_empty[acc_stage]);
           }
           float v[32];
 #pragma unroll
@@ -517,16 +653,29 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           } else if (EPI == kEpiMin) {
-            // kernels/minbmm.cu:86-153: strict '<' in ascending column order keeps the
-            // lowest column on ties; columns past N never compete.
-            if (col0 + 32 <= shape.N) {
+            // kernels/minbmm.cu:86-153 keeps the first index under a strict '<'. Here: the
+            // chunk minimum by a comparison tree, then -- only when it beats the running
+            // best -- the lowest column that holds it. Columns past N never compete.
+            if (col0 + 32 > shape.N) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (v[j] < best) { best = v[j]; best_col = col0 + j; }
-            } else {
+                if (col0 + j >= shape.N) v[j] = INFINITY;
+            }
+            float m16[16], m8[8], m4[4];
 #pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < shape.N && v[j] < best) { best = v[j]; best_col = col0 + j; }
+            for (int j = 0; j < 16; ++j) m16[j] = fminf(v[2 * j], v[2 * j + 1]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) m8[j] = fminf(m16[2 * j], m16[2 * j + 1]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m4[j] = fminf(m8[2 * j], m8[2 * j + 1]);
+            const float m = fminf(fminf(m4[0], m4[1]), fminf(m4[2], m4[3]));
+            if (m < best || (m == best && col0 < best_col)) {
+              best = m;
+              int jj = 0;
+#pragma unroll
+              for (int j = 31; j >= 0; --j)
+                if (v[j] == m) jj = j;
+              best_col = col0 + jj;
             }
           } else {
             // top-k: only values that beat the row's current k-th best are staged; the
@@ -543,7 +692,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                   ++n_staged;
                 }
               }
-              const bool full = n_staged > Traits::kTopkStage - 8;
+              const bool full = n_staged > static_cast<int>(kTopkStageSlots) - 8;
               const uint32_t need = __ballot_sync(0xffffffffu, full);
               if (need) {
                 const uint32_t listed = __ballot_sync(0xffffffffu, has_list);
@@ -556,6 +705,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           }
         }
+        FBMM_PROF_END(1);
         if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
       }
 
@@ -579,6 +729,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
     }
+    if (threadIdx.x == 6 * 32) { FBMM_PROF_FLUSH(12); }
   }
 
   // ------------------------------------------------------------------ teardown
