@@ -337,20 +337,6 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (EPI != kEpiMask) return true;
     return epi.block_mask[b * epi.bm_stride + static_cast<long long>(mb) * epi.bm_cols + t] != 0;
   };
-  // Sweep order inside a unit: CTAs start at different column tiles so that they do not
-  // all ask L2 for the same B tile at the same moment.
-  auto tile_at = [&](int t0, int t1, int i) -> int {
-#ifdef FBMM_ROTATE
-    const int n = t1 - t0;
-    const int rot = static_cast<int>((static_cast<long long>(blockIdx.x) * n) / gridDim.x);
-    int r = i - t0 + rot;
-    if (r >= n) r -= n;
-    return t0 + r;
-#else
-    (void)t0; (void)t1;
-    return i;
-#endif
-  };
   // First and last live tile of a unit; false when the unit has none.
   auto live_range = [&](int b, int mb, int t0, int t1, int& first, int& last) -> bool {
     if (EPI != kEpiMask) { first = t0; last = t1 - 1; return t0 < t1; }
@@ -390,11 +376,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range(b, mb, t0, t1, first, last)) continue;
-        for (int ti = first; ti <= last && ok; ++ti) {
-          const int t = tile_at(t0, t1, ti);
+        for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
           for (int kb = 0; kb < kblocks; ++kb) {
-            if (A_RES && ti == first) {
+            if (A_RES && t == first) {
               // the row block's A k-block, loaded once per unit as soon as the previous
               // unit's last tile has finished with that k-block
               ok = mbar_wait(&bars->a_empty[kb], a_phase ^ 1u, abort_flag);
@@ -450,8 +435,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range(b, mb, t0, t1, first, last)) continue;
-        for (int ti = first; ti <= last && ok; ++ti) {
-          const int t = tile_at(t0, t1, ti);
+        for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
           FBMM_PROF_BEGIN();
           ok = mbar_wait(&bars->acc_empty[acc_stage], acc_phase ^ 1u, abort_flag);
@@ -461,7 +445,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t acc_big = tmem_base + acc_stage * (2 * TILE_N);
           const uint32_t acc_small = acc_big + TILE_N;
           for (int kb = 0; kb < kblocks; ++kb) {
-            if (A_RES && ti == first) {
+            if (A_RES && t == first) {
               ok = mbar_wait(&bars->a_split[kb], a_phase, abort_flag);
               if (!ok) break;
             }
@@ -483,7 +467,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               umma_tf32(acc_small, a_lo, b_hi, idesc, 1u);      // small += A_lo * B_hi
             }
             umma_commit(&bars->empty[stage]);
-            if (A_RES && ti == last) umma_commit(&bars->a_empty[kb]);
+            if (A_RES && t == last) umma_commit(&bars->a_empty[kb]);
             FBMM_PROF_END(2);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
@@ -505,11 +489,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int b, mb, t0, t1, first, last;
       decode(u, b, mb, t0, t1);
       if (!live_range(b, mb, t0, t1, first, last)) continue;
-      for (int ti = first; ti <= last && ok; ++ti) {
-        const int t = tile_at(t0, t1, ti);
+      for (int t = first; t <= last && ok; ++t) {
         if (!tile_live(b, mb, t)) continue;
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (A_RES && ti == first) {
+          if (A_RES && t == first) {
             ok = mbar_wait(&bars->a_full[kb], a_phase, abort_flag);
             if (!ok) break;
             uint8_t* ab = a_region + kb * 2 * kPlaneBytes;
@@ -569,8 +552,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const float* stg_v_w = stg_v + quarter * 32;
       const int* stg_i_w = stg_i + quarter * 32;
 
-      for (int ti = t0; ti < t1 && ok; ++ti) {
-        const int t = tile_at(t0, t1, ti);
+      for (int t = t0; t < t1 && ok; ++t) {
         const int col_tile = t * TILE_N;
         if (!tile_live(b, mb, t)) {
           // masked-out tile: the product is defined as zero (mbmm.py:74 pre-zeroes C).
@@ -669,7 +651,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 4; ++j) m4[j] = fminf(m8[2 * j], m8[2 * j + 1]);
             const float m = fminf(fminf(m4[0], m4[1]), fminf(m4[2], m4[3]));
-            if (m < best || (m == best && col0 < best_col)) {
+            if (m < best) {
               best = m;
               int jj = 0;
 #pragma unroll
