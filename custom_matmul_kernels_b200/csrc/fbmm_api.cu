@@ -79,8 +79,8 @@ int device_state(DeviceState** out) {
     if ((rc = set_smem_attr<kEpiStore, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiMask, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiMin, 1>()) != FBMM_OK) return rc;
+    if ((rc = set_smem_attr<kEpiTopk, 2>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiTopk, 4>()) != FBMM_OK) return rc;
-    if ((rc = set_smem_attr<kEpiTopk, 8>()) != FBMM_OK) return rc;
     st.sms = prop.multiProcessorCount;
     st.ready = true;
   }
@@ -272,10 +272,10 @@ extern "C" {
 int fbmm_version(void) { return 1000; }
 
 #ifdef FBMM_PROFILE
-// Tuning builds only: copies the per-role wait counters of CTA 0 to `out` (16 values).
+// Tuning builds only: copies the per-role wait counters of CTA 0 to `out` (24 values).
 int fbmm_debug_read_profile(long long* out) {
   FBMM_CUDA(cudaDeviceSynchronize());
-  FBMM_CUDA(cudaMemcpyFromSymbol(out, fbmm::g_fbmm_prof, 16 * sizeof(long long)));
+  FBMM_CUDA(cudaMemcpyFromSymbol(out, fbmm::g_fbmm_prof, 24 * sizeof(long long)));
   return FBMM_OK;
 }
 #endif
@@ -444,8 +444,8 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
     e.topk_indices = indices;
     e.topk_chunk_rows = 0;
   }
-  if (topk <= 96) rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e);
-  else rc = launch_gemm<kEpiTopk, 8>(stream, *st, p, s, e);
+  if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e);  // list slots per lane
+  else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e);
   if (rc != FBMM_OK) return rc;
   if (s.n_chunks > 1)
     return fbmm_topk_merge_f32(stream_, e.topk_values, e.topk_indices, s.n_chunks, rows, topk, values, indices);
@@ -459,41 +459,60 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
 // ---------------------------------------------------------------------------------------
 namespace fbmm {
 
+// One warp per row. The running list lives in the output row; each group's list is fed
+// to the rank merge 32 candidates at a time, and because the lists are sorted a group is
+// left as soon as its next candidates cannot beat the current k-th value.
 template <int E>
 __global__ void __launch_bounds__(128) fbmm_topk_merge_kernel(const float* __restrict__ cv, const long long* __restrict__ ci,
-                                                              int groups, long long rows, int k, float* __restrict__ ov,
-                                                              long long* __restrict__ oi) {
+                                                              int groups, long long rows, int k, float* ov, long long* oi) {
   const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;  // whole warps leave together
   const int lane = static_cast<int>(lane_id());
-  float v[E];
-  int ix[E];
-#pragma unroll
-  for (int j = 0; j < E; ++j) { v[j] = -INFINITY; ix[j] = kTopkEmpty; }
-  // slots [0, k): running best; slots [k, 2k): next group's list
-  for (int g = 0; g < groups; ++g) {
-    const float* gv = cv + (static_cast<long long>(g) * rows + row) * k;
-    const long long* gi = ci + (static_cast<long long>(g) * rows + row) * k;
-#pragma unroll
-    for (int j = 0; j < E; ++j) {
-      const int i = j * 32 + lane;
-      if (i >= k) {
-        v[j] = -INFINITY;
-        ix[j] = kTopkEmpty;
-        if (i < 2 * k) {
-          const long long id = gi[i - k];
-          if (id >= 0) { v[j] = gv[i - k]; ix[j] = static_cast<int>(id); }
-        }
-      }
-    }
-    warp_bitonic_sort_desc<E>(v, ix);
-  }
+  float* lv = ov + row * k;
+  long long* li = oi + row * k;
 #pragma unroll
   for (int j = 0; j < E; ++j) {
     const int i = j * 32 + lane;
-    if (i < k) {
-      ov[row * k + i] = v[j];
-      oi[row * k + i] = (ix[j] == kTopkEmpty) ? -1ll : static_cast<long long>(ix[j]);
+    if (i < k) { lv[i] = -INFINITY; li[i] = -1ll; }
+  }
+  __syncwarp();
+  float thr = -INFINITY;
+  for (int g = 0; g < groups; ++g) {
+    const float* gv = cv + (static_cast<long long>(g) * rows + row) * k;
+    const long long* gi = ci + (static_cast<long long>(g) * rows + row) * k;
+    for (int c0 = 0; c0 < k; c0 += 32) {
+      const int i = c0 + lane;
+      float v = -INFINITY;
+      long long id = -1;
+      if (i < k) { v = gv[i]; id = gi[i]; }
+      const bool pass = id >= 0 && v > thr;
+      const uint32_t pm = __ballot_sync(0xffffffffu, pass);
+      if (pm == 0) break;  // sorted: nothing further in this group can enter
+      // compact the passing candidates to lanes [0, cnt)
+      const int cnt = __popc(pm);
+      const int dst = __popc(pm & ((1u << lane) - 1u));
+      float cvv = -INFINITY;
+      int cii = kTopkEmpty;
+      for (int s = 0; s < 32; ++s) {
+        const float sv = __shfl_sync(0xffffffffu, v, s);
+        const int si = __shfl_sync(0xffffffffu, static_cast<int>(id), s);
+        const int sd = __shfl_sync(0xffffffffu, dst, s);
+        if (((pm >> s) & 1u) && sd == lane) { cvv = sv; cii = si; }
+      }
+      float L[E];
+      int LI[E];
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const int q = j * 32 + lane;
+        L[j] = -INFINITY;
+        LI[j] = kTopkEmpty;
+        if (q < k) {
+          L[j] = lv[q];
+          const long long t = li[q];
+          LI[j] = t < 0 ? kTopkEmpty : static_cast<int>(t);
+        }
+      }
+      thr = topk_rank_merge<E>(L, LI, cvv, cii, cnt, k, lv, li, 0);
     }
   }
 }
@@ -509,10 +528,10 @@ extern "C" int fbmm_topk_merge_f32(void* stream, const float* cand_values, const
   const long long blocks = (rows + 3) / 4;
   if (blocks > 0x7fffffffll) return fail(FBMM_ERR_INVALID, "too many rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (2 * topk <= 128)
-    fbmm::fbmm_topk_merge_kernel<4><<<static_cast<unsigned>(blocks), 128, 0, s>>>(cand_values, cand_indices, groups, rows, topk, out_values, out_indices);
+  if (topk <= 64)
+    fbmm::fbmm_topk_merge_kernel<2><<<static_cast<unsigned>(blocks), 128, 0, s>>>(cand_values, cand_indices, groups, rows, topk, out_values, out_indices);
   else
-    fbmm::fbmm_topk_merge_kernel<8><<<static_cast<unsigned>(blocks), 128, 0, s>>>(cand_values, cand_indices, groups, rows, topk, out_values, out_indices);
+    fbmm::fbmm_topk_merge_kernel<4><<<static_cast<unsigned>(blocks), 128, 0, s>>>(cand_values, cand_indices, groups, rows, topk, out_values, out_indices);
   FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
 }

@@ -42,18 +42,28 @@ __device__ unsigned int g_fbmm_status[4];
 
 // Optional per-role wait-time counters (cycles), compiled in only for tuning builds.
 #ifdef FBMM_PROFILE
-__device__ long long g_fbmm_prof[16];
-#define FBMM_PROF_DECL long long prof_t0_ = 0, prof_acc_[4] = {0, 0, 0, 0}
+__device__ long long g_fbmm_prof[24];
+#define FBMM_PROF_DECL long long prof_t0_ = 0, prof_acc_[4] = {0, 0, 0, 0}, prof_x_[4] = {0, 0, 0, 0}, prof_x0_ = 0
+#define FBMM_PROF_XBEGIN() prof_x0_ = clock64()
+#define FBMM_PROF_XEND(i) prof_x_[i] += clock64() - prof_x0_
+#define FBMM_PROF_XFLUSH() if (blockIdx.x == 0) { for (int q_ = 0; q_ < 4; ++q_) g_fbmm_prof[16 + q_] = prof_x_[q_]; }
 #define FBMM_PROF_BEGIN() prof_t0_ = clock64()
 #define FBMM_PROF_END(i) prof_acc_[i] += clock64() - prof_t0_
+#define FBMM_PROF_MARK(i, c, n) long long prof_m0_ = clock64(); prof_acc_[c] += (n)
+#define FBMM_PROF_MARK_END(i) prof_acc_[i] += clock64() - prof_m0_
 #define FBMM_PROF_FLUSH(base)                                                           \
   if (blockIdx.x == 0) {                                                                \
     for (int q_ = 0; q_ < 4; ++q_) g_fbmm_prof[(base) + q_] = prof_acc_[q_];            \
   }
 #else
 #define FBMM_PROF_DECL
+#define FBMM_PROF_XBEGIN()
+#define FBMM_PROF_XEND(i)
+#define FBMM_PROF_XFLUSH()
 #define FBMM_PROF_BEGIN()
 #define FBMM_PROF_END(i)
+#define FBMM_PROF_MARK(i, c, n)
+#define FBMM_PROF_MARK_END(i)
 #define FBMM_PROF_FLUSH(base)
 #endif
 
@@ -146,23 +156,93 @@ __device__ __forceinline__ void warp_bitonic_sort_desc(float (&v)[E], int (&ix)[
   }
 }
 
-// Merges, for every row of this warp flagged in `need`, the row's staged candidates
-// into its running list (k entries, descending, kept in the output buffers) and returns
-// the caller lane's new threshold (the k-th best) when its own row was flagged, else
-// `thr` unchanged. Rows are handled one after the other by the whole warp: list and
-// staged entries are spread over the lanes, sorted by the bitonic network, and the first
-// k written back. `has_list` flags rows whose list has been written before; the others
-// start from an empty list (-inf / -1 padding). Called by all 32 lanes.
-//   lv0 / li0: list of the warp's first row; stg_v / stg_i: staging, slot-major
-//   [slot][128 rows], already offset to the warp's first row.
-// Plays the part of bitonic_sort_128 + bitonic_sort_256 under the row mutex in the
-// reference (kernels/topkbmm.cu:98-183), without the mutex: a row has one owner.
 constexpr int kTopkEmpty = 0x7fffffff;
 
+// Stores the staged candidate (x, col) as one 8-byte entry at shared-memory byte address
+// `addr` when `pred` is non-zero; predicated, so a warp never diverges over it.
+__device__ __forceinline__ void topk_stage_if(uint32_t pred, uint32_t addr, float x, int col) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.u32 p, %0, 0;\n"
+      "@p st.shared.v2.b32 [%1], {%2, %3};\n"
+      "}\n"
+      ::"r"(pred), "r"(addr), "r"(__float_as_uint(x)), "r"(col)
+      : "memory");
+}
+
+// Rank merge of up to 32 unsorted candidates (one per lane, lanes [0, cnt)) into a
+// descending list of k entries spread over the warp (entry i in lane i % 32, slot i / 32).
+// Every list entry moves down by the number of candidates that precede it, every
+// candidate lands at (list entries that precede it) + (candidates that precede it);
+// positions >= k fall off the end. The new list is scattered to lv / li (list storage,
+// indices written with `index_offset` added) and the new k-th value is returned to all
+// lanes. Order: larger value first, ties by lower index; empty slots (-inf, kTopkEmpty)
+// sort last. Takes the place of the reference's sort-then-merge networks
+// (bitonic_sort_128 + bitonic_sort_256, kernels/topkbmm.cu:98-183): the list is already
+// sorted and only a few candidates arrive at a time, so ranking them costs O(cnt) per
+// lane instead of a full sorting network.
+template <int E>
+__device__ __forceinline__ float topk_rank_merge(const float (&L)[E], const int (&LI)[E], float cv, int ci, int cnt,
+                                                 int k, float* lv, long long* li, long long index_offset) {
+  const int lane = static_cast<int>(lane_id());
+  int add[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) add[j] = 0;
+  int my_pos = 0;
+  for (int c = 0; c < cnt; ++c) {
+    const float bv = __shfl_sync(0xffffffffu, cv, c);
+    const int bi = __shfl_sync(0xffffffffu, ci, c);
+    int list_before = 0;
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      const bool cand_first = topk_before(bv, bi, L[j], LI[j]);
+      add[j] += cand_first ? 1 : 0;
+      const bool slot = (j * 32 + lane) < k;
+      list_before += __popc(__ballot_sync(0xffffffffu, slot && !cand_first));
+    }
+    if (lane == c) my_pos += list_before;
+    else if (lane < cnt && topk_before(bv, bi, cv, ci)) my_pos += 1;
+  }
+  __syncwarp();
+  float kth = -INFINITY;
+  bool have = false;
+#pragma unroll
+  for (int j = 0; j < E; ++j) {
+    const int i = j * 32 + lane;
+    const int p = i + add[j];
+    if (i < k && p < k) {
+      if (add[j] != 0) {  // unmoved entries are already in place
+        lv[p] = L[j];
+        li[p] = (LI[j] == kTopkEmpty) ? -1ll : static_cast<long long>(LI[j]) + index_offset;
+      }
+      if (p == k - 1) { kth = L[j]; have = true; }
+    }
+  }
+  if (lane < cnt && my_pos < k) {
+    lv[my_pos] = cv;
+    li[my_pos] = static_cast<long long>(ci) + index_offset;
+    if (my_pos == k - 1) { kth = cv; have = true; }
+  }
+  const uint32_t who = __ballot_sync(0xffffffffu, have);
+  kth = __shfl_sync(0xffffffffu, kth, who ? (__ffs(who) - 1) : 0);
+  __syncwarp();
+  return kth;
+}
+
+// Merges, for every row of this warp flagged in `need`, the row's staged candidates
+// (at most 32) into its running list (k entries, descending, kept in the output
+// buffers) and returns the caller lane's new threshold (the k-th best) when its own row
+// was flagged, else `thr` unchanged. Rows are handled one after the other by the whole
+// warp. `has_list` flags rows whose list has been written before; the others start from
+// an empty list (-inf / -1 padding). Called by all 32 lanes.
+//   lv0 / li0: list of the warp's first row; stg: staging entries (value bits, column),
+//   slot-major [slot][128 rows], already offset to the warp's first row. A row has one owner, so no
+//   lock is needed (the reference takes a per-row spin mutex, kernels/topkbmm.cu:13-47).
 template <int E>
 __device__ __noinline__ float topk_merge_rows(uint32_t need, uint32_t has_list, int n_staged, float thr,
                                               float* lv0, long long* li0, int k, long long index_offset,
-                                              const float* stg_v, const int* stg_i) {
+                                              const int2* stg) {
   const int lane = static_cast<int>(lane_id());
   uint32_t m = need;
   while (m) {
@@ -172,44 +252,41 @@ __device__ __noinline__ float topk_merge_rows(uint32_t need, uint32_t has_list, 
     const bool listed = (has_list >> src) & 1u;
     float* lv = lv0 + static_cast<long long>(src) * k;
     long long* li = li0 + static_cast<long long>(src) * k;
-    float v[E];
-    int ix[E];
+    float L[E];
+    int LI[E];
 #pragma unroll
     for (int j = 0; j < E; ++j) {
       const int i = j * 32 + lane;
-      v[j] = -INFINITY;
-      ix[j] = kTopkEmpty;
-      if (i < k) {
-        if (listed) {
-          v[j] = lv[i];
-          const long long gi = li[i];
-          ix[j] = gi < 0 ? kTopkEmpty : static_cast<int>(gi - index_offset);
-        }
-      } else if (i - k < cnt) {
-        v[j] = stg_v[(i - k) * kTileM + src];
-        ix[j] = stg_i[(i - k) * kTileM + src];
+      L[j] = -INFINITY;
+      LI[j] = kTopkEmpty;
+      if (i < k && listed) {
+        L[j] = lv[i];
+        const long long gi = li[i];
+        LI[j] = gi < 0 ? kTopkEmpty : static_cast<int>(gi - index_offset);
       }
     }
-    warp_bitonic_sort_desc<E>(v, ix);
-    float kth = -INFINITY;
+    float cv = -INFINITY;
+    int ci = kTopkEmpty;
+    if (lane < cnt) {
+      const int2 e = stg[lane * kTileM + src];
+      cv = __int_as_float(e.x);
+      ci = e.y;
+    }
+    if (!listed) {
+      // first write of this row: lay down the padding the rank merge will not touch
 #pragma unroll
-    for (int j = 0; j < E; ++j) {
-      const int i = j * 32 + lane;
-      if (i < k) {
-        lv[i] = v[j];
-        li[i] = (ix[j] == kTopkEmpty) ? -1ll : static_cast<long long>(ix[j]) + index_offset;
+      for (int j = 0; j < E; ++j) {
+        const int i = j * 32 + lane;
+        if (i < k) { lv[i] = -INFINITY; li[i] = -1ll; }
       }
-      if (j == ((k - 1) >> 5)) kth = v[j];
+      __syncwarp();
     }
-    kth = __shfl_sync(0xffffffffu, kth, (k - 1) & 31);
+    const float kth = topk_rank_merge<E>(L, LI, cv, ci, cnt, k, lv, li, index_offset);
     if (lane == src) thr = kth;
   }
   return thr;
 }
 
-// --------------------------------------------------------------------------------------
-// the kernel
-// --------------------------------------------------------------------------------------
 // Shared-memory plan, computed identically on the host (launch size) and in the kernel.
 //   [A region: kblocks x (hi 16 KB | lo 16 KB)]      only when A stays resident
 //   [ring: stages x stage_bytes]                     stage = (A hi | A lo |) B hi | B lo
@@ -528,9 +605,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool ok = true;
     FBMM_PROF_DECL;
 
-    // top-k staging (slot-major): values then indices
-    float* stg_v = reinterpret_cast<float*>(epi_smem);
-    int* stg_i = reinterpret_cast<int*>(epi_smem + kTopkStageSlots * kTileM * 4);
+    // top-k staging: 8-byte (value, column) entries, slot-major [slot][row]
+    int2* stg = reinterpret_cast<int2*>(epi_smem);
 
     for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
       int b, mb, t0, t1;
@@ -541,16 +617,17 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // per-unit reduction state
       float best = INFINITY;
       int best_col = t0 * TILE_N;
-      float thr = -INFINITY;  // top-k: current k-th best of this row
-      int n_staged = 0;
+      // top-k: current k-th best of this row (+inf for rows past M, which never stage)
+      float thr = row_ok ? -INFINITY : INFINITY;
+      const uint32_t stg_base = smem_u32(stg + row_in_tile);
+      uint32_t stg_slot = stg_base;  // address of this row's next free staging slot
       bool has_list = false;
       // list of this warp's first row (rows of a warp are consecutive)
       const long long warp_row0 = (shape.tiles_per_chunk > 0 ? (t0 / shape.tiles_per_chunk) : 0) * epi.topk_chunk_rows +
                                   static_cast<long long>(b) * shape.M + mb * kTileM + static_cast<int>(quarter) * 32;
       float* lv0 = (EPI == kEpiTopk) ? epi.topk_values + warp_row0 * epi.k : nullptr;
       long long* li0 = (EPI == kEpiTopk) ? epi.topk_indices + warp_row0 * epi.k : nullptr;
-      const float* stg_v_w = stg_v + quarter * 32;
-      const int* stg_i_w = stg_i + quarter * 32;
+      const int2* stg_w = stg + quarter * 32;
 
       for (int t = t0; t < t1 && ok; ++t) {
         const int col_tile = t * TILE_N;
@@ -579,9 +656,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll 1
         for (int c = 0; c < TILE_N / 32; ++c) {
           uint32_t rb[32], rs[32];
+          FBMM_PROF_XBEGIN();
           tmem_ld_32x32b_x32(acc_big + c * 32, rb);
           tmem_ld_32x32b_x32(acc_small + c * 32, rs);
           tmem_ld_wait();
+          FBMM_PROF_XEND(0);
+          FBMM_PROF_XBEGIN();
           if (c == TILE_N / 32 - 1) {
             // both accumulators of this stage are now in registers: hand the stage back
             tcgen05_fence_before_sync();
@@ -661,31 +741,45 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
           } else {
             // top-k: only values that beat the row's current k-th best are staged; the
-            // stage is merged into the row's list before it can overflow.
-            const int valid = shape.N - col0;  // columns of this chunk that exist
+            // stage is merged into the row's list before it can overflow. Groups of 8
+            // columns in which no row of the warp has a candidate are skipped outright.
+            constexpr int kSlotStride = kTileM * 8;
+            if (col0 + 32 > shape.N) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j >= shape.N) v[j] = -INFINITY;  // never greater than a threshold
+            }
 #pragma unroll
             for (int j0 = 0; j0 < 32; j0 += 8) {
+              const float mx = fmaxf(fmaxf(fmaxf(v[j0], v[j0 + 1]), fmaxf(v[j0 + 2], v[j0 + 3])),
+                                     fmaxf(fmaxf(v[j0 + 4], v[j0 + 5]), fmaxf(v[j0 + 6], v[j0 + 7])));
+              if (__any_sync(0xffffffffu, mx > thr)) {
+                uint32_t hit = 0;
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const int jj = j0 + j;
-                if (row_ok && jj < valid && v[jj] > thr) {
-                  stg_v[n_staged * kTileM + row_in_tile] = v[jj];
-                  stg_i[n_staged * kTileM + row_in_tile] = col0 + jj;
-                  ++n_staged;
+                for (int j = 0; j < 8; ++j) hit |= (v[j0 + j] > thr ? 1u : 0u) << j;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  topk_stage_if((hit >> j) & 1u, stg_slot + __popc(hit & ((1u << j) - 1u)) * kSlotStride, v[j0 + j],
+                                col0 + j0 + j);
+                stg_slot += __popc(hit) * kSlotStride;
+                // at most 8 slots were taken since the last check: merge while 8 are still free
+                const int n_staged = static_cast<int>(stg_slot - stg_base) / kSlotStride;
+                const bool full = n_staged > static_cast<int>(kTopkStageSlots) - 8;
+                const uint32_t need = __ballot_sync(0xffffffffu, full);
+                if (need) {
+                  const uint32_t listed = __ballot_sync(0xffffffffu, has_list);
+                  __syncwarp();
+                  FBMM_PROF_MARK(2, 3, __popc(need));
+                  thr = topk_merge_rows<TOPK_E>(need, listed, n_staged, thr, lv0, li0, epi.k, epi.index_offset,
+                                                stg_w);
+                  FBMM_PROF_MARK_END(2);
+                  if (full) { stg_slot = stg_base; has_list = true; }
+                  __syncwarp();
                 }
-              }
-              const bool full = n_staged > static_cast<int>(kTopkStageSlots) - 8;
-              const uint32_t need = __ballot_sync(0xffffffffu, full);
-              if (need) {
-                const uint32_t listed = __ballot_sync(0xffffffffu, has_list);
-                __syncwarp();
-                thr = topk_merge_rows<TOPK_E>(need, listed, n_staged, thr, lv0, li0, epi.k, epi.index_offset,
-                                              stg_v_w, stg_i_w);
-                if (full) { n_staged = 0; has_list = true; }
-                __syncwarp();
               }
             }
           }
+          FBMM_PROF_XEND(1);
         }
         FBMM_PROF_END(1);
         if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
@@ -701,17 +795,18 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       } else if (EPI == kEpiTopk) {
         if (ok) {
+          const int n_staged = static_cast<int>(stg_slot - stg_base) / (kTileM * 8);
           const bool pending = row_ok && (n_staged > 0 || !has_list);
           const uint32_t need = __ballot_sync(0xffffffffu, pending);
           const uint32_t listed = __ballot_sync(0xffffffffu, has_list);
           __syncwarp();
           if (need)
             thr = topk_merge_rows<TOPK_E>(need, listed, n_staged, thr, lv0, li0, epi.k, epi.index_offset,
-                                          stg_v_w, stg_i_w);
+                                          stg_w);
         }
       }
     }
-    if (threadIdx.x == 6 * 32) { FBMM_PROF_FLUSH(12); }
+    if (threadIdx.x == 6 * 32) { FBMM_PROF_FLUSH(12); FBMM_PROF_XFLUSH(); }
   }
 
   // ------------------------------------------------------------------ teardown
