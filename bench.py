@@ -276,6 +276,17 @@ def algorithmic_bytes(name, units):
     return units * k * 4 + k * n * 4 + units * TOPK * 12
 
 
+def measured_traffic(name, units):
+    """DRAM bytes per launch from the ncu capture summarised in profiles/ (c4 min kernel at
+    262 144 rows: 171.38 MB read + 6.21 MB written), scaled per row: A and the outputs grow
+    with the rows, the 33.55 MB of B do not. None where no capture has been taken."""
+    if name != "c4":
+        return None
+    b_bytes = 128 * 65536 * 4
+    per_row = (171.377152e6 + 6.21312e6 - b_bytes) / 262144.0
+    return b_bytes + units * per_row
+
+
 def cpu_baseline(name):
     """Reference semantics on the host cores over a bounded sample (rank 0, N=1)."""
     from oracle import ref_semantics as R
@@ -401,7 +412,7 @@ def run_ours(args):
                     "peak_note": f"{peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} / 2 (tf32) / 3 "
                                  "(three tf32 MMAs per fp32 product)"}
         roof["frac"] = roof["achieved"] / roof["peak"]
-        roof["traffic"] = None
+        roof["traffic"] = measured_traffic(name, wl.h["units"])
         roof["kernel"] = "fbmm_gemm_kernel"
         if world == 1:
             roof["tf32_cublas_tflops_live"] = measure_tf32_cublas()
