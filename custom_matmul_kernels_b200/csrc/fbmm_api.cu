@@ -535,3 +535,76 @@ extern "C" int fbmm_topk_merge_f32(void* stream, const float* cand_values, const
   FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// min_bmm without caller scratch and without any allocation
+// ---------------------------------------------------------------------------------------
+// Some hosts that embed this library through the C ABI cannot allocate device memory at
+// call time: a serving loop whose memory budget is fixed at start-up, or a plugin host that
+// hands an operator its input and output buffers and nothing else and has no torch caching
+// allocator to ask. cudaMalloc there would synchronise the device and may simply fail. For
+// them the packed-key scratch of min_bmm (8 bytes per output row) lives in this
+// file-scope device array instead of a caller workspace. Every GPU that loads the library
+// holds these 2 MiB until the process exits.
+#define FBMM_NOALLOC_MAX_ROWS 262144
+static __device__ __align__(256) unsigned long long g_noalloc_min_keys[FBMM_NOALLOC_MAX_ROWS];
+
+namespace {
+// Device address of g_noalloc_min_keys per device. In host code the array's name is only a
+// stand-in for the symbol, not a device pointer, so the address a kernel may use has to be
+// asked for with cudaGetSymbolAddress while that device is current.
+unsigned long long* g_noalloc_keys_addr[kMaxDevices] = {nullptr};
+std::mutex g_noalloc_mu;
+
+int noalloc_keys_for_current_device(unsigned long long** out) {
+  int dev = 0;
+  FBMM_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(FBMM_ERR_INVALID, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_keys_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    FBMM_CUDA(cudaGetSymbolAddress(&ptr, g_noalloc_min_keys));
+    if (ptr == nullptr) return fail(FBMM_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_noalloc_keys_addr[dev] = static_cast<unsigned long long*>(ptr);
+  }
+  *out = g_noalloc_keys_addr[dev];
+  return FBMM_OK;
+}
+}  // namespace
+
+extern "C" int fbmm_min_bmm_f32_noalloc(void* stream_, const float* A, int a_layout, long long lda, long long stride_a,
+                                        const float* B, int b_layout, long long ldb, long long stride_b, float* values,
+                                        long long* indices, int l, int m, int n, int k, int dim) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
+  RowProblem p;
+  if ((rc = make_row_problem(&p, A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
+  if ((rc = check_operand("A", dim == 2 ? p.a : p.b, k, l)) != FBMM_OK) return rc;
+  if ((rc = check_operand("B", dim == 2 ? p.b : p.a, k, l)) != FBMM_OK) return rc;
+  const long long rows = static_cast<long long>(l) * p.M;
+  if (rows > FBMM_NOALLOC_MAX_ROWS)
+    return fail(FBMM_ERR_WORKSPACE,
+                "fbmm_min_bmm_f32_noalloc handles at most %d output rows per call (l * rows), got %lld; "
+                "split the call or use fbmm_min_bmm_f32 with a caller workspace",
+                FBMM_NOALLOC_MAX_ROWS, rows);
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  unsigned long long* keys = nullptr;
+  if ((rc = noalloc_keys_for_current_device(&keys)) != FBMM_OK) return rc;
+  GemmShape s = base_shape(p);
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  // The array keeps the previous call's keys: every key this call will reduce into must
+  // start at all-ones again.
+  FBMM_CUDA(cudaMemsetAsync(keys, 0xff, static_cast<size_t>(rows) * 8, stream));
+  EpiArgs e{};
+  e.keys = keys;
+  if ((rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e)) != FBMM_OK) return rc;
+  const int threads = 256;
+  const long long blocks = (rows + threads - 1) / threads;
+  fbmm_min_finalize_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(keys, values, indices, rows);
+  FBMM_CUDA(cudaGetLastError());
+  return FBMM_OK;
+}

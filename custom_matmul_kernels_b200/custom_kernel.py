@@ -43,6 +43,8 @@ SIGNATURES = {
     "fbmm_min_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_min_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                          _c_ptr, _c_size]),
+    "fbmm_min_bmm_f32_noalloc": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                                                                 _c_int]),
     "fbmm_topk_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_topk_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                           _c_int, _c_ll, _c_ptr, _c_size]),

@@ -90,6 +90,27 @@ int fbmm_min_bmm_f32(void* stream,
                      int l, int m, int n, int k, int dim,
                      void* workspace, size_t workspace_bytes);
 
+/* min_bmm for callers that cannot allocate device memory and cannot supply scratch: a
+ * serving loop with a memory budget frozen at start-up, or a plugin host that passes an
+ * operator only its inputs and outputs (no torch allocator, and a cudaMalloc at call time
+ * would synchronise the device or fail). Same arguments and results as fbmm_min_bmm_f32
+ * minus the workspace; the 8-byte-per-row key scratch lives in a 2 MiB device array inside
+ * the library (held by every GPU that loads it, until exit). It has no counterpart in the
+ * reference.
+ *  - Limit: l * (m for dim 2, n for dim 1) <= 262144 output rows per call; more returns
+ *    FBMM_ERR_WORKSPACE with a message naming the limit.
+ *  - Calls no cudaMalloc / cudaFree or allocating library routine. The first call on a
+ *    device looks the array's address up (cudaGetSymbolAddress) and sets kernel
+ *    attributes; make that first call outside any stream capture.
+ *  - All calls on a device share the one array: calls whose kernels overlap on the GPU
+ *    (different streams) race on it. Calls on one stream are safe; each clears the keys
+ *    it uses before reducing into them. */
+int fbmm_min_bmm_f32_noalloc(void* stream,
+                             const float* A, int a_layout, long long lda, long long stride_a,
+                             const float* B, int b_layout, long long ldb, long long stride_b,
+                             float* values, long long* indices,
+                             int l, int m, int n, int k, int dim);
+
 /* Largest-`topk` entries (descending) and their indices per row (dim = 2, output
  * [l, m, topk]) or per column (dim = 1, output [l, n, topk]) of A @ B. Replaces
  * topk_bmm_nn/nt/tn/tt (kernels/topkbmm.cu:500,403,306,597) with topk_dim_2 / topk_dim_1
