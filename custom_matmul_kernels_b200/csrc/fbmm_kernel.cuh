@@ -156,6 +156,32 @@ __device__ __forceinline__ void warp_bitonic_sort_desc(float (&v)[E], int (&ix)[
   }
 }
 
+// Within each group of four lanes, turns "lane q holds 32 consecutive columns of its own
+// row" into "lane q holds columns [8q, 8q+8) of each of the group's four rows":
+// afterwards v[8i .. 8i+7] belongs to row (group base + i). A warp store of v[8i..] then
+// writes eight complete 128-byte lines (four lanes per line) instead of touching 32 lines
+// with one sector each, which is what the load/store unit is short of when the output is
+// written at HBM speed. Two butterfly stages, 32 shuffles.
+__device__ __forceinline__ void transpose_rows_in_lane_quads(float (&v)[32]) {
+  const bool hi2 = (lane_id() & 2u) != 0;
+  const bool hi1 = (lane_id() & 1u) != 0;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const float send = hi2 ? v[j] : v[16 + j];
+    const float recv = __shfl_xor_sync(0xffffffffu, send, 2);
+    if (hi2) v[j] = recv; else v[16 + j] = recv;
+  }
+#pragma unroll
+  for (int h = 0; h < 32; h += 16) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float send = hi1 ? v[h + j] : v[h + 8 + j];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+      if (hi1) v[h + j] = recv; else v[h + 8 + j] = recv;
+    }
+  }
+}
+
 constexpr int kTopkEmpty = 0x7fffffff;
 
 // Stores the staged candidate (x, col) as one 8-byte entry at shared-memory byte address
@@ -605,6 +631,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bool ok = true;
     FBMM_PROF_DECL;
 
+    // 256-bit stores need every row start of C 32-byte aligned
+    const bool c_lines_ok = (EPI == kEpiStore || EPI == kEpiMask) && ((epi.ldc & 7) == 0) &&
+                            ((epi.stride_c & 7) == 0) && ((reinterpret_cast<uintptr_t>(epi.C) & 31) == 0);
+    // 8-byte reads of the element mask need its rows 8-byte aligned
+    const bool em_lines_ok = (EPI == kEpiMask) && ((shape.N & 7) == 0) && ((epi.em_stride & 7) == 0) &&
+                             ((reinterpret_cast<uintptr_t>(epi.element_mask) & 7) == 0);
     // top-k staging: 8-byte (value, column) entries, slot-major [slot][row]
     int2* stg = reinterpret_cast<int2*>(epi_smem);
 
@@ -633,15 +665,24 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int col_tile = t * TILE_N;
         if (!tile_live(b, mb, t)) {
           // masked-out tile: the product is defined as zero (mbmm.py:74 pre-zeroes C).
-          if (EPI == kEpiMask && row_ok) {
-            float* crow = epi.C + b * epi.stride_c + static_cast<long long>(row) * epi.ldc;
+          if (EPI == kEpiMask) {
             const int c_end = min(shape.N, col_tile + TILE_N);
-            const bool vec = ((epi.ldc & 3) == 0) && ((epi.stride_c & 3) == 0) &&
-                             ((reinterpret_cast<uintptr_t>(epi.C) & 15) == 0);
-            int c = col_tile;
-            if (vec)
-              for (; c + 4 <= c_end; c += 4) __stcs(reinterpret_cast<float4*>(crow + c), make_float4(0.f, 0.f, 0.f, 0.f));
-            for (; c < c_end; ++c) crow[c] = 0.f;
+            if (c_lines_ok && col_tile + TILE_N <= shape.N) {
+              // four lanes per row: every store instruction writes eight whole lines
+              const int q = static_cast<int>(lane & 3u);
+              const int row_g = mb * kTileM + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
+              float* cbase = epi.C + b * epi.stride_c + static_cast<long long>(row_g) * epi.ldc + col_tile + 8 * q;
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (row_g + i < shape.M)
+#pragma unroll
+                  for (int c = 0; c < TILE_N; c += 32)
+                    st_global_v8_streaming(cbase + static_cast<long long>(i) * epi.ldc + c, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f,
+                                           0.f, 0.f);
+            } else if (row_ok) {
+              float* crow = epi.C + b * epi.stride_c + static_cast<long long>(row) * epi.ldc;
+              for (int c = col_tile; c < c_end; ++c) crow[c] = 0.f;
+            }
           }
           continue;
         }
@@ -673,38 +714,64 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int col0 = col_tile + c * 32;
 
           if (EPI == kEpiStore || EPI == kEpiMask) {
-            if (row_ok && col0 < shape.N) {
+            const bool line_path = c_lines_ok && col0 + 32 <= shape.N && (EPI != kEpiMask || em_lines_ok);
+            if (line_path) {
+              // Whole warp (rows past M included: their lanes still carry the shuffles).
+              // After the transpose lane q of each lane quad holds columns [8q, 8q+8) of
+              // the quad's four rows, so masks are read and C is written 4 lanes per row.
+              transpose_rows_in_lane_quads(v);
+              const int q = static_cast<int>(lane & 3u);
+              const int row_g = mb * kTileM + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
+              float* cbase = epi.C + b * epi.stride_c + static_cast<long long>(row_g) * epi.ldc + col0 + 8 * q;
               if (EPI == kEpiMask) {
-                // kernels/mbmm.cu:360-363 (8x8 tile skip) and :111-133 (element multiply)
+                // kernels/mbmm.cu:360-363 (8x8 tile skip) and :111-133 (element multiply);
+                // all mask bytes are fetched before the first store so the loads overlap
+                unsigned char tmv[4];
+                uint2 e8[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int r = min(row_g + i, shape.M - 1);
+                  tmv[i] = epi.thread_mask[b * epi.tm_stride + static_cast<long long>(r >> 3) * epi.tm_cols +
+                                           (col0 >> 3) + q];
+                  e8[i] = *reinterpret_cast<const uint2*>(epi.element_mask + b * epi.em_stride +
+                                                          static_cast<long long>(r) * shape.N + col0 + 8 * q);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    const uint32_t w = j < 4 ? e8[i].x : e8[i].y;
+                    const float ef = static_cast<float>((w >> ((j & 3) * 8)) & 0xffu);
+                    v[8 * i + j] = tmv[i] != 0 ? v[8 * i + j] * ef : 0.f;
+                  }
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 4; ++i)
+                if (row_g + i < shape.M)
+                  st_global_v8_streaming(cbase + static_cast<long long>(i) * epi.ldc, v[8 * i], v[8 * i + 1],
+                                         v[8 * i + 2], v[8 * i + 3], v[8 * i + 4], v[8 * i + 5], v[8 * i + 6],
+                                         v[8 * i + 7]);
+            } else if (row_ok && col0 < shape.N) {
+              // ragged right edge or storage that is not 32-byte friendly: one row per thread
+              if (EPI == kEpiMask) {
                 const unsigned char* tm = epi.thread_mask + b * epi.tm_stride +
                                           static_cast<long long>(row >> 3) * epi.tm_cols + (col0 >> 3);
                 const unsigned char* em = epi.element_mask + b * epi.em_stride +
                                           static_cast<long long>(row) * shape.N + col0;
-                const bool em_vec = ((reinterpret_cast<uintptr_t>(em) & 15) == 0) && (col0 + 32 <= shape.N);
-                unsigned char e[32];
-                if (em_vec) {
-                  const uint4 e0 = *reinterpret_cast<const uint4*>(em);
-                  const uint4 e1 = *reinterpret_cast<const uint4*>(em + 16);
-                  const uint32_t w[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-#pragma unroll
-                  for (int j = 0; j < 32; ++j) e[j] = static_cast<unsigned char>((w[j >> 2] >> ((j & 3) * 8)) & 0xffu);
-                } else {
-#pragma unroll
-                  for (int j = 0; j < 32; ++j) e[j] = (col0 + j < shape.N) ? em[j] : 0;
-                }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                   const bool tlive = (col0 + g * 8 < shape.N) ? (tm[g] != 0) : false;
 #pragma unroll
                   for (int j = 0; j < 8; ++j) {
                     const int jj = g * 8 + j;
-                    v[jj] = tlive ? v[jj] * static_cast<float>(e[jj]) : 0.f;
+                    const float ef = (col0 + jj < shape.N) ? static_cast<float>(em[jj]) : 0.f;
+                    v[jj] = tlive ? v[jj] * ef : 0.f;
                   }
                 }
               }
               float* crow = epi.C + b * epi.stride_c + static_cast<long long>(row) * epi.ldc + col0;
-              const bool vec = ((reinterpret_cast<uintptr_t>(crow) & 15) == 0) && (col0 + 32 <= shape.N);
-              if (vec) {
+              if (col0 + 32 <= shape.N && (reinterpret_cast<uintptr_t>(crow) & 15) == 0) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                   __stcs(reinterpret_cast<float4*>(crow + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));

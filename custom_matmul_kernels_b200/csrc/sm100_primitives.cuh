@@ -234,6 +234,17 @@ __device__ __forceinline__ void tmem_ld_wait() {
 }
 
 // ----------------------------------------------------------------------------------
+// 256-bit global store (sm_100): one thread writes a whole 32-byte sector; the address
+// must be 32-byte aligned. Streaming (evict-first) because the output is not re-read.
+// ----------------------------------------------------------------------------------
+__device__ __forceinline__ void st_global_v8_streaming(float* p, float a0, float a1, float a2, float a3, float a4,
+                                                       float a5, float a6, float a7) {
+  asm volatile("st.global.cs.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(a0), "f"(a1), "f"(a2),
+               "f"(a3), "f"(a4), "f"(a5), "f"(a6), "f"(a7)
+               : "memory");
+}
+
+// ----------------------------------------------------------------------------------
 // fp32 -> (hi, lo) split for 3xTF32. The tensor core reads only the sign, exponent and
 // top 10 mantissa bits of a tf32 operand, so hi = x with the low 13 mantissa bits
 // cleared is exactly what the MMA sees when it is handed x itself, and lo = x - hi is
