@@ -49,10 +49,16 @@ EncodeTiledFn g_encode = nullptr;
 
 template <int EPI, int E>
 int set_smem_attr() {
-  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kSmemLimit)));
-  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kSmemLimit)));
+  if (EPI == kEpiMin || EPI == kEpiTopk) {
+    FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kSmemLimit)));
+    FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(kSmemLimit)));
+  }
   return FBMM_OK;
 }
 
@@ -230,22 +236,84 @@ constexpr int kMinOverheadTiles = 1;
 constexpr int kTopkOverheadTiles = 12;
 constexpr int kMaxChunks = 64;
 
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Number of floats between an operand's first and last element, storage gaps included.
+long long operand_span(const Operand& op, int k, int l) {
+  const long long outer = op.mn_major ? k : op.rows;
+  const long long inner = op.mn_major ? op.rows : k;
+  return (l > 1 ? static_cast<long long>(l - 1) * op.stride : 0) + (outer - 1) * op.ld + inner;
+}
+
+// Pre-splitting pays when every operand tile is fetched many times (each lo plane costs one
+// extra read and write of the operand) and the storage has no large gaps.
+bool presplit_worthwhile(const RowProblem& p) {
+  if (p.M < 1024 || p.N < 1024) return false;
+  // The column operand streams past every row block. Its hi and lo planes together must
+  // stay L2-sized: the CTAs drift apart over a long sweep, and a stream that L2 cannot
+  // hold is then re-read from HBM per CTA, where doubling it costs more than it saves.
+  if (operand_span(p.b, p.K, p.L) * 8 > 96ll * 1024 * 1024) return false;
+  const long long dense_a = static_cast<long long>(p.L) * p.M * p.K, dense_b = static_cast<long long>(p.L) * p.N * p.K;
+  return operand_span(p.a, p.K, p.L) <= 2 * dense_a && operand_span(p.b, p.K, p.L) <= 2 * dense_b;
+}
+
+size_t presplit_bytes(const RowProblem& p) {
+  return align_up(static_cast<size_t>(operand_span(p.a, p.K, p.L)) * 4, 256) +
+         align_up(static_cast<size_t>(operand_span(p.b, p.K, p.L)) * 4, 256);
+}
+
+// Launches the fused kernel. `lo_scratch` (or null) is room for the lo planes of both
+// operands (presplit_bytes): when given, they are computed here by one element-wise pass
+// each and the kernel runs without its splitter stage.
 template <int EPI, int E>
-int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p, GemmShape shape, const EpiArgs& epi) {
-  CUtensorMap ta, tb;
+int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p, GemmShape shape, const EpiArgs& epi,
+                void* lo_scratch = nullptr) {
+  CUtensorMap ta, tb, ta_lo, tb_lo;
   int rc;
   if ((rc = make_tensor_map(&ta, p.a, p.K, p.L, kTileM)) != FBMM_OK) return rc;
   if ((rc = make_tensor_map(&tb, p.b, p.K, p.L, kTileN)) != FBMM_OK) return rc;
+  const bool presplit = lo_scratch != nullptr && (EPI == kEpiMin || EPI == kEpiTopk);
+  if (presplit) {
+    const long long span_a = operand_span(p.a, p.K, p.L), span_b = operand_span(p.b, p.K, p.L);
+    float* a_lo = static_cast<float*>(lo_scratch);
+    float* b_lo = reinterpret_cast<float*>(static_cast<char*>(lo_scratch) + align_up(static_cast<size_t>(span_a) * 4, 256));
+    const int threads = 256;
+    const int blocks = st.sms * 8;
+    fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.a.ptr, a_lo, span_a);
+    fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.b.ptr, b_lo, span_b);
+    FBMM_CUDA(cudaGetLastError());
+    Operand oa = p.a, ob = p.b;
+    oa.ptr = a_lo;
+    ob.ptr = b_lo;
+    if ((rc = make_tensor_map(&ta_lo, oa, p.K, p.L, kTileM)) != FBMM_OK) return rc;
+    if ((rc = make_tensor_map(&tb_lo, ob, p.K, p.L, kTileN)) != FBMM_OK) return rc;
+  } else {
+    ta_lo = ta;
+    tb_lo = tb;
+  }
   const long long grid = shape.num_units < st.sms ? shape.num_units : st.sms;
   const int kblocks = (p.K + kKBlock - 1) / kKBlock;
   // Up to K = 128 the row block of A stays in shared memory for the whole unit.
   const bool a_resident = kblocks <= kMaxResidentKBlocks;
   const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk);
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
-  if (a_resident)
-    fbmm_gemm_kernel<EPI, E, true><<<static_cast<unsigned>(grid), kNumThreads, plan.total, stream>>>(ta, tb, shape, epi);
-  else
-    fbmm_gemm_kernel<EPI, E, false><<<static_cast<unsigned>(grid), kNumThreads, plan.total, stream>>>(ta, tb, shape, epi);
+  const unsigned g = static_cast<unsigned>(grid);
+  if (EPI == kEpiMin || EPI == kEpiTopk) {
+    constexpr int EP = (EPI == kEpiMin || EPI == kEpiTopk) ? EPI : kEpiMin;  // keeps the store kernels out of this branch
+    if (presplit && a_resident)
+      fbmm_gemm_kernel<EP, E, true, true><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
+    else if (presplit)
+      fbmm_gemm_kernel<EP, E, false, true><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
+    else if (a_resident)
+      fbmm_gemm_kernel<EP, E, true, false><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
+    else
+      fbmm_gemm_kernel<EP, E, false, false><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
+  } else {
+    if (a_resident)
+      fbmm_gemm_kernel<EPI, E, true, false><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
+    else
+      fbmm_gemm_kernel<EPI, E, false, false><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
+  }
   FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
 }
@@ -259,8 +327,6 @@ GemmShape base_shape(const RowProblem& p) {
   s.n_tiles = (p.N + kTileN - 1) / kTileN;
   return s;
 }
-
-size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 }  // namespace
 
@@ -366,7 +432,7 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   const size_t need = fbmm_min_bmm_workspace_bytes(l, m, n, k, dim);
   if (workspace == nullptr || workspace_bytes < need)
     return fail(FBMM_ERR_WORKSPACE, "min_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
-  if ((reinterpret_cast<uintptr_t>(workspace) & 7u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 8-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 16-byte aligned");
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
@@ -377,12 +443,27 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   FBMM_CUDA(cudaMemsetAsync(keys, 0xff, static_cast<size_t>(rows) * 8, stream));
   EpiArgs e{};
   e.keys = keys;
-  if ((rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e)) != FBMM_OK) return rc;
+  // room behind the keys for the lo planes? then the operands are split once up front
+  void* lo_scratch = nullptr;
+  const size_t lo_off = align_up(need, 256);
+  if (presplit_worthwhile(p) && workspace_bytes >= lo_off + presplit_bytes(p)) lo_scratch = static_cast<char*>(workspace) + lo_off;
+  if ((rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e, lo_scratch)) != FBMM_OK) return rc;
   const int threads = 256;
   const long long blocks = (rows + threads - 1) / threads;
   fbmm_min_finalize_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(keys, values, indices, rows);
   FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
+}
+
+size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k, int a_layout, long long lda, long long stride_a,
+                                     int b_layout, long long ldb, long long stride_b) {
+  if (l <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
+  RowProblem p;
+  if (make_row_problem(&p, nullptr, a_layout, lda, stride_a, nullptr, b_layout, ldb, stride_b, l, m, n, k, 2) != FBMM_OK)
+    return 0;
+  if (p.a.ld < (p.a.mn_major ? m : k) || p.b.ld < (p.b.mn_major ? n : k)) return 0;
+  if (!presplit_worthwhile(p)) return 0;
+  return presplit_bytes(p);
 }
 
 static void topk_plan(int l, int rows_per_batch, int cols, int sms, int* n_chunks, int* tiles_per_chunk) {
@@ -444,8 +525,17 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
     e.topk_indices = indices;
     e.topk_chunk_rows = 0;
   }
-  if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e);  // list slots per lane
-  else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e);
+  size_t own = 0;
+  if (s.n_chunks > 1) {
+    const size_t entries = static_cast<size_t>(s.n_chunks) * rows * topk;
+    own = align_up(align_up(entries * sizeof(float), 256) + entries * sizeof(long long), 256);
+  }
+  void* lo_scratch = nullptr;
+  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && presplit_worthwhile(p) &&
+      workspace_bytes >= own + presplit_bytes(p))
+    lo_scratch = static_cast<char*>(workspace) + own;
+  if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch);  // list slots per lane
+  else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e, lo_scratch);
   if (rc != FBMM_OK) return rc;
   if (s.n_chunks > 1)
     return fbmm_topk_merge_f32(stream_, e.topk_values, e.topk_indices, s.n_chunks, rows, topk, values, indices);

@@ -367,9 +367,13 @@ __device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint
   }
 }
 
-template <int EPI, int TOPK_E, bool A_RES>
+// PRESPLIT: the lo planes of A and B were computed once by fbmm_split_lo_kernel into global
+// scratch with the operands' own strides; TMA then brings hi and lo, the splitter warps
+// stand idle and a ring stage is ready the moment its copies land.
+template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_a_lo, const __grid_constant__ CUtensorMap tmap_b_lo,
                  const GemmShape shape, const EpiArgs epi) {
   constexpr int TILE_N = kTileN;
   constexpr int kAccStages = 2;
@@ -413,6 +417,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (PRESPLIT) {
+      tma_prefetch_desc(&tmap_a_lo);
+      tma_prefetch_desc(&tmap_b_lo);
+    }
   }
   if (warp == 1) {
     tmem_alloc(&bars->tmem_base, kTmemCols);
@@ -449,22 +457,22 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     return first >= 0;
   };
 
-  auto load_a = [&](uint8_t* dst, uint64_t* bar, int kb, int mb, int b) {
+  auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb, int mb, int b) {
     if (!shape.a_mn) {
-      tma_load_3d(dst, &tmap_a, bar, kb * kKBlock, mb * kTileM, b);
+      tma_load_3d(dst, map, bar, kb * kKBlock, mb * kTileM, b);
     } else {
 #pragma unroll
       for (int c = 0; c < kTileM / 32; ++c)
-        tma_load_3d(dst + c * 4096, &tmap_a, bar, mb * kTileM + c * 32, kb * kKBlock, b);
+        tma_load_3d(dst + c * 4096, map, bar, mb * kTileM + c * 32, kb * kKBlock, b);
     }
   };
-  auto load_b = [&](uint8_t* dst, uint64_t* bar, int kb, int t, int b) {
+  auto load_b = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb, int t, int b) {
     if (!shape.b_mn) {
-      tma_load_3d(dst, &tmap_b, bar, kb * kKBlock, t * TILE_N, b);
+      tma_load_3d(dst, map, bar, kb * kKBlock, t * TILE_N, b);
     } else {
 #pragma unroll
       for (int c = 0; c < TILE_N / 32; ++c)
-        tma_load_3d(dst + c * 4096, &tmap_b, bar, t * TILE_N + c * 32, kb * kKBlock, b);
+        tma_load_3d(dst + c * 4096, map, bar, t * TILE_N + c * 32, kb * kKBlock, b);
     }
   };
 
@@ -487,17 +495,22 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               // unit's last tile has finished with that k-block
               ok = mbar_wait(&bars->a_empty[kb], a_phase ^ 1u, abort_flag);
               if (!ok) break;
-              mbar_arrive_expect_tx(&bars->a_full[kb], kPlaneBytes);
-              load_a(a_region + kb * 2 * kPlaneBytes, &bars->a_full[kb], kb, mb, b);
+              mbar_arrive_expect_tx(&bars->a_full[kb], PRESPLIT ? 2 * kPlaneBytes : kPlaneBytes);
+              load_a(&tmap_a, a_region + kb * 2 * kPlaneBytes + off_a_hi, &bars->a_full[kb], kb, mb, b);
+              if (PRESPLIT) load_a(&tmap_a_lo, a_region + kb * 2 * kPlaneBytes + off_a_lo, &bars->a_full[kb], kb, mb, b);
             }
             FBMM_PROF_BEGIN();
             ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag);
             FBMM_PROF_END(0);
             if (!ok) break;
             uint8_t* sb = ring + stage * plan.stage_bytes;
-            mbar_arrive_expect_tx(&bars->full[stage], A_RES ? kPlaneBytes : 2 * kPlaneBytes);
-            if (!A_RES) load_a(sb + off_a_hi, &bars->full[stage], kb, mb, b);
-            load_b(sb + off_b_hi, &bars->full[stage], kb, t, b);
+            mbar_arrive_expect_tx(&bars->full[stage], (A_RES ? 1u : 2u) * (PRESPLIT ? 2u : 1u) * kPlaneBytes);
+            if (!A_RES) {
+              load_a(&tmap_a, sb + off_a_hi, &bars->full[stage], kb, mb, b);
+              if (PRESPLIT) load_a(&tmap_a_lo, sb + off_a_lo, &bars->full[stage], kb, mb, b);
+            }
+            load_b(&tmap_b, sb + off_b_hi, &bars->full[stage], kb, t, b);
+            if (PRESPLIT) load_b(&tmap_b_lo, sb + off_b_lo, &bars->full[stage], kb, t, b);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
         }
@@ -549,11 +562,11 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t acc_small = acc_big + TILE_N;
           for (int kb = 0; kb < kblocks; ++kb) {
             if (A_RES && t == first) {
-              ok = mbar_wait(&bars->a_split[kb], a_phase, abort_flag);
+              ok = mbar_wait(PRESPLIT ? &bars->a_full[kb] : &bars->a_split[kb], a_phase, abort_flag);
               if (!ok) break;
             }
             FBMM_PROF_BEGIN();
-            ok = mbar_wait(&bars->split[stage], phase, abort_flag);
+            ok = mbar_wait(PRESPLIT ? &bars->full[stage] : &bars->split[stage], phase, abort_flag);
             FBMM_PROF_END(1);
             if (!ok) break;
             tcgen05_fence_after_sync();
@@ -584,6 +597,9 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ hi/lo splitters
+    if (PRESPLIT) {
+      // nothing to split: the lo planes arrive by TMA
+    } else {
     const int st = static_cast<int>(threadIdx.x) - 64;
     uint32_t stage = 0, phase = 0, a_phase = 0;
     bool ok = true;
@@ -622,6 +638,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       a_phase ^= 1u;
     }
     if (st == 0) { FBMM_PROF_FLUSH(8); }
+    }
   } else {
     // ------------------------------------------------------------------ epilogue
     const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read
@@ -884,6 +901,21 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tcgen05_fence_after_sync();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+}
+
+// lo plane of a whole operand: lo[i] = x[i] - tf32(x[i]) over `count` floats (both pointers
+// 16-byte aligned; the last count % 4 floats are handled one by one).
+__global__ void fbmm_split_lo_kernel(const float* __restrict__ src, float* __restrict__ lo, long long count) {
+  const long long count4 = count >> 2;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  const float4* src4 = reinterpret_cast<const float4*>(src);
+  float4* lo4 = reinterpret_cast<float4*>(lo);
+  for (long long i = tid; i < count4; i += stride) {
+    const float4 x = src4[i];
+    lo4[i] = make_float4(split_lo(x.x), split_lo(x.y), split_lo(x.z), split_lo(x.w));
+  }
+  if (tid < (count & 3)) lo[4 * count4 + tid] = split_lo(src[4 * count4 + tid]);
 }
 
 // keys -> (values, indices) for min_bmm

@@ -45,6 +45,8 @@ SIGNATURES = {
                                                          _c_ptr, _c_size]),
     "fbmm_min_bmm_f32_noalloc": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                                                  _c_int]),
+    "fbmm_presplit_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _c_ll,
+                                                _c_ll]),
     "fbmm_topk_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_topk_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                           _c_int, _c_ll, _c_ptr, _c_size]),

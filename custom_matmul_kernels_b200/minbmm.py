@@ -51,8 +51,11 @@ class MinBMMCUDA(CustomKernel):
         indices = torch.empty((l, rows), device=A3.device, dtype=torch.int64)
         a_keep, a_t, lda, sa = operand(A3)
         b_keep, b_t, ldb, sb = operand(B3)
-        ws_bytes = self.lib.fbmm_min_bmm_workspace_bytes(l, m, n, k, dim)
-        ws = torch.empty(max(ws_bytes, 8), device=A3.device, dtype=torch.uint8)
+        # own scratch (packed keys) plus, for large problems, room for pre-split lo planes
+        ws_bytes = (self.lib.fbmm_min_bmm_workspace_bytes(l, m, n, k, dim) + 255) // 256 * 256
+        ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, k, layout_letter(a_t, False), lda, sa,
+                                                           layout_letter(b_t, True), ldb, sb)
+        ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
         with torch.cuda.device(A3.device):
             check(self.lib.fbmm_min_bmm_f32(
                 self.stream_ptr(A3.device),

@@ -55,7 +55,10 @@ class TopkBMMCUDA(CustomKernel):
         a_keep, a_t, lda, sa = operand(A3)
         b_keep, b_t, ldb, sb = operand(B3)
         with torch.cuda.device(A3.device):
-            ws_bytes = self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim)
+            # own scratch (per-chunk lists) plus, for large problems, room for pre-split lo planes
+            ws_bytes = (self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim) + 255) // 256 * 256
+            ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, d, layout_letter(a_t, False), lda, sa,
+                                                               layout_letter(b_t, True), ldb, sb)
             ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
             check(self.lib.fbmm_topk_bmm_f32(
                 self.stream_ptr(A3.device),

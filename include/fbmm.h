@@ -111,6 +111,19 @@ int fbmm_min_bmm_f32_noalloc(void* stream,
                              float* values, long long* indices,
                              int l, int m, int n, int k, int dim);
 
+/* Optional extra scratch for fbmm_min_bmm_f32 and fbmm_topk_bmm_f32. The kernels form every
+ * fp32 product from three tf32 products of (hi, lo) operand planes; normally the lo planes
+ * are produced in shared memory tile by tile. When the caller's workspace has this many
+ * bytes beyond the op's own need (rounded up to 256), the lo planes of A and B are computed
+ * once into that room instead, which pays when every tile is fetched many times. Returns 0
+ * for shapes where it would not be used (fewer than 1024 rows or columns, or storage with
+ * large gaps, or a column operand whose two planes exceed 96 MB and would fall out of L2).
+ * Same answers either way. No reference counterpart (its kernels multiply in
+ * fp32 on the CUDA cores, kernels/bmm_helpers.cu:20-26). */
+size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k,
+                                     int a_layout, long long lda, long long stride_a,
+                                     int b_layout, long long ldb, long long stride_b);
+
 /* Largest-`topk` entries (descending) and their indices per row (dim = 2, output
  * [l, m, topk]) or per column (dim = 1, output [l, n, topk]) of A @ B. Replaces
  * topk_bmm_nn/nt/tn/tt (kernels/topkbmm.cu:500,403,306,597) with topk_dim_2 / topk_dim_1

@@ -278,3 +278,42 @@ def test_c_abi_min_workspace_too_small(dev, lib):
     rc = lib.fbmm_min_bmm_f32(None, A.data_ptr(), ord("n"), 32, 0, B.data_ptr(), ord("n"), 128, 0, v.data_ptr(),
                               i.data_ptr(), 1, 128, 128, 32, 2, ws.data_ptr(), 64)
     assert rc == ck.FBMM_ERR_WORKSPACE
+
+
+def test_presplit_scratch_gives_identical_bits(dev, lib):
+    """With room for pre-split lo planes in the workspace the kernels skip their in-kernel
+    splitter; the planes hold the same values either way, so the outputs must not differ
+    in a single bit (min with K <= 128, top-k with K > 128)."""
+    g = torch.Generator().manual_seed(31)
+    stream = torch.cuda.current_stream().cuda_stream
+    for (m, k, n) in [(1100, 96, 1300), (1024, 160, 1536)]:
+        A = torch.randn(1, m, k, generator=g).to(dev)
+        B = torch.randn(1, k, n, generator=g).to(dev)
+        extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, ord("n"), k, m * k, ord("n"), n, k * n)
+        assert extra >= (m * k + k * n) * 4
+        outs = []
+        for use_extra in (False, True):
+            own = (lib.fbmm_min_bmm_workspace_bytes(1, m, n, k, 2) + 255) // 256 * 256
+            nbytes = own + (extra if use_extra else 0)
+            ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+            v = torch.empty(1, m, device=dev)
+            i = torch.empty(1, m, device=dev, dtype=torch.int64)
+            rc = lib.fbmm_min_bmm_f32(stream, A.data_ptr(), ord("n"), k, m * k, B.data_ptr(), ord("n"), n, k * n,
+                                      v.data_ptr(), i.data_ptr(), 1, m, n, k, 2, ws.data_ptr(), nbytes)
+            assert rc == 0, lib.fbmm_last_error()
+            own_t = (lib.fbmm_topk_bmm_workspace_bytes(1, m, n, k, 16, 2) + 255) // 256 * 256
+            nb_t = own_t + (extra if use_extra else 0)
+            ws_t = torch.empty(max(nb_t, 256), device=dev, dtype=torch.uint8)
+            tv = torch.empty(1, m, 16, device=dev)
+            ti = torch.empty(1, m, 16, device=dev, dtype=torch.int64)
+            rc = lib.fbmm_topk_bmm_f32(stream, A.data_ptr(), ord("n"), k, m * k, B.data_ptr(), ord("n"), n, k * n,
+                                       tv.data_ptr(), ti.data_ptr(), 1, m, n, k, 16, 2, 0, ws_t.data_ptr(), nb_t)
+            assert rc == 0, lib.fbmm_last_error()
+            torch.cuda.synchronize()
+            outs.append((v, i, tv, ti))
+        for a, b in zip(*outs):
+            assert torch.equal(a, b)
+        R.check_min(outs[1][0], outs[1][1], A.cpu(), B.cpu(), 2)
+        R.check_topk(outs[1][2], outs[1][3], A.cpu(), B.cpu(), 16, 2)
+    assert lib.fbmm_presplit_workspace_bytes(1, 512, 4096, 64, ord("n"), 64, 0, ord("n"), 4096, 0) == 0
+    assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
