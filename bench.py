@@ -181,6 +181,10 @@ class Workload:
         elif name in ("c1", "c4"):
             self.op = MinBMMCUDA()
             self.kernels_per_step = 2   # fused GEMM+min kernel, key-unpack kernel
+            l_, m_, k_ = self.A.shape
+            n_ = self.B.shape[2]
+            if self.op.lib.fbmm_presplit_workspace_bytes(l_, m_, n_, k_, ord("n"), k_, m_ * k_, ord("n"), n_, k_ * n_):
+                self.kernels_per_step += 2  # one lo-plane pass per operand
         else:
             self.op = TopkBMMCUDA()
             self.kernels_per_step = 1 + (1 if world > 1 else 0)  # + candidate merge
@@ -277,14 +281,14 @@ def algorithmic_bytes(name, units):
 
 
 def measured_traffic(name, units):
-    """DRAM bytes per launch from the ncu capture summarised in profiles/ (c4 min kernel at
-    262 144 rows: 171.38 MB read + 6.21 MB written), scaled per row: A and the outputs grow
-    with the rows, the 33.55 MB of B do not. None where no capture has been taken."""
+    """DRAM bytes per launch from the ncu capture summarised in profiles/ (c4 min kernel with
+    pre-split lo planes at 262 144 rows: 875.0 MB read + 5.7 MB written), scaled by the rows
+    processed: A hi+lo and the outputs grow with the rows, and B (hi+lo 67 MB, just over what
+    L2 keeps between sweeps) is re-read from HBM roughly once per wave of row blocks, which
+    also grows with the rows. None where no capture has been taken."""
     if name != "c4":
         return None
-    b_bytes = 128 * 65536 * 4
-    per_row = (171.377152e6 + 6.21312e6 - b_bytes) / 262144.0
-    return b_bytes + units * per_row
+    return units * (875.006208e6 + 5.70624e6) / 262144.0
 
 
 def cpu_baseline(name):

@@ -457,22 +457,26 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     return first >= 0;
   };
 
+  // The column operand is re-read by every row block, so it should outlive everything
+  // else in L2. A resident row block of A is read exactly once (first out); a streamed one
+  // is re-read for every column tile of the unit and keeps the default priority.
+  const uint64_t a_policy = A_RES ? kL2EvictFirst : kL2EvictLast;
   auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb, int mb, int b) {
     if (!shape.a_mn) {
-      tma_load_3d(dst, map, bar, kb * kKBlock, mb * kTileM, b);
+      tma_load_3d(dst, map, bar, kb * kKBlock, mb * kTileM, b, a_policy);
     } else {
 #pragma unroll
       for (int c = 0; c < kTileM / 32; ++c)
-        tma_load_3d(dst + c * 4096, map, bar, mb * kTileM + c * 32, kb * kKBlock, b);
+        tma_load_3d(dst + c * 4096, map, bar, mb * kTileM + c * 32, kb * kKBlock, b, a_policy);
     }
   };
   auto load_b = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb, int t, int b) {
     if (!shape.b_mn) {
-      tma_load_3d(dst, map, bar, kb * kKBlock, t * TILE_N, b);
+      tma_load_3d(dst, map, bar, kb * kKBlock, t * TILE_N, b, kL2EvictLast);
     } else {
 #pragma unroll
       for (int c = 0; c < TILE_N / 32; ++c)
-        tma_load_3d(dst + c * 4096, map, bar, t * TILE_N + c * 32, kb * kKBlock, b);
+        tma_load_3d(dst + c * 4096, map, bar, t * TILE_N + c * 32, kb * kKBlock, b, kL2EvictLast);
     }
   };
 

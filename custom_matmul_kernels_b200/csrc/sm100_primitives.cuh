@@ -106,13 +106,18 @@ __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }
 
+// L2 eviction-priority policies for TMA loads (createpolicy encodings): data that is read
+// once per sweep should leave L2 first, data that every CTA re-reads should leave last.
+constexpr uint64_t kL2EvictFirst = 0x12F0000000000000ull;
+constexpr uint64_t kL2EvictLast = 0x14F0000000000000ull;
+
 __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, uint64_t* bar,
-                                            int32_t c0, int32_t c1, int32_t c2) {
+                                            int32_t c0, int32_t c1, int32_t c2, uint64_t l2_policy) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5}], [%2];"
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4, %5}], [%2], %6;"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)),
-        "r"(c0), "r"(c1), "r"(c2)
+        "r"(c0), "r"(c1), "r"(c2), "l"(l2_policy)
       : "memory");
 }
 
