@@ -262,6 +262,38 @@ size_t presplit_bytes(const RowProblem& p) {
          align_up(static_cast<size_t>(operand_span(p.b, p.K, p.L)) * 4, 256);
 }
 
+size_t norms_bytes(const RowProblem& p) {
+  return align_up(static_cast<size_t>(p.L) * p.M * 4, 256) + align_up(static_cast<size_t>(p.L) * p.N * 4, 256);
+}
+
+// Squared norms of both operands of a row-form problem into `scratch` (norms_bytes);
+// fills the epilogue arguments.
+int launch_norms(cudaStream_t stream, const RowProblem& p, void* scratch, EpiArgs* e) {
+  float* rn = static_cast<float*>(scratch);
+  float* cn = reinterpret_cast<float*>(static_cast<char*>(scratch) + align_up(static_cast<size_t>(p.L) * p.M * 4, 256));
+  const Operand* ops[2] = {&p.a, &p.b};
+  float* outs[2] = {rn, cn};
+  for (int i = 0; i < 2; ++i) {
+    const Operand& op = *ops[i];
+    const long long total = static_cast<long long>(p.L) * op.rows;
+    const int threads = 256;
+    const long long work = op.mn_major ? total : total * 32;
+    const long long blocks = (work + threads - 1) / threads;
+    fbmm_sqnorm_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(op.ptr, outs[i], p.L, op.rows, p.K, op.ld,
+                                                                              p.L > 1 ? op.stride : 0, op.mn_major ? 1 : 0);
+  }
+  FBMM_CUDA(cudaGetLastError());
+  e->row_norms = rn;
+  e->col_norms = cn;
+  return FBMM_OK;
+}
+
+int check_distance(int distance) {
+  if (distance != FBMM_DIST_INNER && distance != FBMM_DIST_L2)
+    return fail(FBMM_ERR_INVALID, "distance must be FBMM_DIST_INNER (0) or FBMM_DIST_L2 (1), got %d", distance);
+  return FBMM_OK;
+}
+
 // Launches the fused kernel. `lo_scratch` (or null) is room for the lo planes of both
 // operands (presplit_bytes): when given, they are computed here by one element-wise pass
 // each and the kernel runs without its splitter stage.
@@ -411,25 +443,29 @@ int fbmm_mbmm_f32(void* stream, const float* A, int a_layout, long long lda, lon
   return launch_gemm<kEpiMask, 1>(static_cast<cudaStream_t>(stream), *st, p, s, e);
 }
 
-size_t fbmm_min_bmm_workspace_bytes(int l, int m, int n, int k, int dim) {
+size_t fbmm_min_bmm_workspace_bytes(int l, int m, int n, int k, int dim, int distance) {
   (void)k;
   if (l <= 0 || m <= 0 || n <= 0) return 0;
   const long long rows = static_cast<long long>(l) * (dim == 1 ? n : m);
-  return static_cast<size_t>(rows) * sizeof(unsigned long long);
+  size_t need = static_cast<size_t>(rows) * sizeof(unsigned long long);
+  if (distance == FBMM_DIST_L2)
+    need = align_up(need, 256) + align_up(static_cast<size_t>(l) * m * 4, 256) + align_up(static_cast<size_t>(l) * n * 4, 256);
+  return need;
 }
 
 int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
                      int b_layout, long long ldb, long long stride_b, float* values, long long* indices, int l, int m,
-                     int n, int k, int dim, void* workspace, size_t workspace_bytes) {
+                     int n, int k, int dim, int distance, void* workspace, size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   int rc;
   if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if ((rc = check_distance(distance)) != FBMM_OK) return rc;
   if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
   RowProblem p;
   if ((rc = make_row_problem(&p, A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
   if ((rc = check_operand("A", dim == 2 ? p.a : p.b, k, l)) != FBMM_OK) return rc;
   if ((rc = check_operand("B", dim == 2 ? p.b : p.a, k, l)) != FBMM_OK) return rc;
-  const size_t need = fbmm_min_bmm_workspace_bytes(l, m, n, k, dim);
+  const size_t need = fbmm_min_bmm_workspace_bytes(l, m, n, k, dim, distance);
   if (workspace == nullptr || workspace_bytes < need)
     return fail(FBMM_ERR_WORKSPACE, "min_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
   if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 16-byte aligned");
@@ -443,7 +479,10 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   FBMM_CUDA(cudaMemsetAsync(keys, 0xff, static_cast<size_t>(rows) * 8, stream));
   EpiArgs e{};
   e.keys = keys;
-  // room behind the keys for the lo planes? then the operands are split once up front
+  if (distance == FBMM_DIST_L2 &&
+      (rc = launch_norms(stream, p, static_cast<char*>(workspace) + align_up(static_cast<size_t>(rows) * 8, 256), &e)) != FBMM_OK)
+    return rc;
+  // room behind the op's own scratch for the lo planes? then the operands are split once up front
   void* lo_scratch = nullptr;
   const size_t lo_off = align_up(need, 256);
   if (presplit_worthwhile(p) && workspace_bytes >= lo_off + presplit_bytes(p)) lo_scratch = static_cast<char*>(workspace) + lo_off;
@@ -472,15 +511,20 @@ static void topk_plan(int l, int rows_per_batch, int cols, int sms, int* n_chunk
   choose_chunks(l, m_blocks, n_tiles, sms, kTopkOverheadTiles, kMaxChunks, n_chunks, tiles_per_chunk);
 }
 
-size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim) {
+size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim, int distance) {
   (void)k;
   if (l <= 0 || m <= 0 || n <= 0 || topk <= 0) return 0;
   const int rows_pb = dim == 1 ? n : m, cols = dim == 1 ? m : n;
   int n_chunks, tpc;
   topk_plan(l, rows_pb, cols, sm_count_or_default(), &n_chunks, &tpc);
-  if (n_chunks <= 1) return 0;
-  const size_t entries = static_cast<size_t>(n_chunks) * l * rows_pb * topk;
-  return align_up(entries * sizeof(float), 256) + entries * sizeof(long long);
+  size_t need = 0;
+  if (n_chunks > 1) {
+    const size_t entries = static_cast<size_t>(n_chunks) * l * rows_pb * topk;
+    need = align_up(entries * sizeof(float), 256) + entries * sizeof(long long);
+  }
+  if (distance == FBMM_DIST_L2)
+    need = align_up(need, 256) + align_up(static_cast<size_t>(l) * m * 4, 256) + align_up(static_cast<size_t>(l) * n * 4, 256);
+  return need;
 }
 
 int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long* cand_indices, int groups,
@@ -488,11 +532,12 @@ int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long*
 
 int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
                       int b_layout, long long ldb, long long stride_b, float* values, long long* indices, int l, int m,
-                      int n, int k, int topk, int dim, long long index_offset, void* workspace,
+                      int n, int k, int topk, int dim, int distance, long long index_offset, void* workspace,
                       size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   int rc;
   if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if ((rc = check_distance(distance)) != FBMM_OK) return rc;
   if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
   if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
   RowProblem p;
@@ -529,6 +574,15 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
   if (s.n_chunks > 1) {
     const size_t entries = static_cast<size_t>(s.n_chunks) * rows * topk;
     own = align_up(align_up(entries * sizeof(float), 256) + entries * sizeof(long long), 256);
+  }
+  if (distance == FBMM_DIST_L2) {
+    const size_t need = own + norms_bytes(p);
+    if (workspace == nullptr || workspace_bytes < need)
+      return fail(FBMM_ERR_WORKSPACE, "topk_bmm with l2 distance needs %zu workspace bytes, got %zu", need, workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+      return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
+    if ((rc = launch_norms(stream, p, static_cast<char*>(workspace) + own, &e)) != FBMM_OK) return rc;
+    own = need;
   }
   void* lo_scratch = nullptr;
   if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && presplit_worthwhile(p) &&

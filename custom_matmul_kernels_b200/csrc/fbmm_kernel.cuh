@@ -95,6 +95,10 @@ struct EpiArgs {
   int k;
   long long index_offset;     // added to every column index written (column shards)
   long long topk_chunk_rows;  // rows between the lists of consecutive column chunks (0: one chunk)
+  // squared-l2 distance (min / top-k): squared norms of the row operand [L][M] and of the
+  // column operand [L][N]; null for the inner product
+  const float* row_norms;
+  const float* col_norms;
 };
 
 // Order-preserving map fp32 -> uint32 (smaller float <=> smaller key).
@@ -667,6 +671,9 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int row = mb * kTileM + row_in_tile;
       const bool row_ok = row < shape.M;
 
+      // squared-l2 mode: this row's squared norm
+      const bool l2 = (EPI == kEpiMin || EPI == kEpiTopk) && epi.row_norms != nullptr;
+      const float row_norm = (l2 && row_ok) ? epi.row_norms[static_cast<long long>(b) * shape.M + row] : 0.f;
       // per-unit reduction state
       float best = INFINITY;
       int best_col = t0 * TILE_N;
@@ -733,6 +740,27 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rb[j]) + __uint_as_float(rs[j]);
           const int col0 = col_tile + c * 32;
+          if (l2) {
+            // squared_l2 of the reference (kernels/bmm_helpers.cu:28-35) in GEMM form:
+            // |a - b|^2 = |a|^2 + |b|^2 - 2 a.b, clamped at 0 against cancellation.
+            const float* cn = epi.col_norms + static_cast<long long>(b) * shape.N + col0;
+            if (col0 + 32 <= shape.N && (reinterpret_cast<uintptr_t>(cn) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) {
+                const float4 n4 = __ldg(reinterpret_cast<const float4*>(cn + j));
+                v[j] = fmaxf(fmaf(-2.f, v[j], row_norm + n4.x), 0.f);
+                v[j + 1] = fmaxf(fmaf(-2.f, v[j + 1], row_norm + n4.y), 0.f);
+                v[j + 2] = fmaxf(fmaf(-2.f, v[j + 2], row_norm + n4.z), 0.f);
+                v[j + 3] = fmaxf(fmaf(-2.f, v[j + 3], row_norm + n4.w), 0.f);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float nj = (col0 + j < shape.N) ? __ldg(cn + j) : 0.f;
+                v[j] = fmaxf(fmaf(-2.f, v[j], row_norm + nj), 0.f);
+              }
+            }
+          }
 
           if (EPI == kEpiStore || EPI == kEpiMask) {
             const bool line_path = c_lines_ok && col0 + 32 <= shape.N && (EPI != kEpiMask || em_lines_ok);
@@ -920,6 +948,38 @@ __global__ void fbmm_split_lo_kernel(const float* __restrict__ src, float* __res
     lo4[i] = make_float4(split_lo(x.x), split_lo(x.y), split_lo(x.z), split_lo(x.w));
   }
   if (tid < (count & 3)) lo[4 * count4 + tid] = split_lo(src[4 * count4 + tid]);
+}
+
+// Squared norms of the rows of an operand: out[l][r] = sum_k x[l][r][k]^2. `ld` is the pitch
+// of the stored rows; mn_major != 0 means the storage runs along r (element (r, k) at
+// k * ld + r), else along k (r * ld + k). One warp per row for k-contiguous storage, one
+// thread per row otherwise; both read coalesced.
+__global__ void fbmm_sqnorm_kernel(const float* __restrict__ x, float* __restrict__ out, int L, int rows, int K,
+                                   long long ld, long long stride, int mn_major) {
+  const long long total = static_cast<long long>(L) * rows;
+  if (mn_major) {
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float* p = x + (i / rows) * stride + (i % rows);
+    float acc = 0.f;
+    for (int k = 0; k < K; ++k) {
+      const float a = p[static_cast<long long>(k) * ld];
+      acc = fmaf(a, a, acc);
+    }
+    out[i] = acc;
+  } else {
+    const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    if (i >= total) return;  // whole warps leave together
+    const float* p = x + (i / rows) * stride + (i % rows) * ld;
+    float acc = 0.f;
+    for (int k = static_cast<int>(lane_id()); k < K; k += 32) {
+      const float a = p[k];
+      acc = fmaf(a, a, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane_id() == 0) out[i] = acc;
+  }
 }
 
 // keys -> (values, indices) for min_bmm

@@ -24,6 +24,21 @@ FBMM_ERR_WORKSPACE = -3
 FBMM_ERR_CUDA = -4
 FBMM_ERR_DEVICE = -5
 FBMM_ERR_UNSUPPORTED = -6
+FBMM_DIST_INNER = 0
+FBMM_DIST_L2 = 1
+
+
+def distance_code(distance: str) -> int:
+    """The reference's `distance` strings (minbmm.py:12-19): inner and l2 are built; l1 has
+    no matrix-product form and stays unimplemented; anything else is an error (the
+    reference builds that ValueError but never raises it, minbmm.py:19)."""
+    if distance == "inner":
+        return FBMM_DIST_INNER
+    if distance in ("l2", "euclidean"):
+        return FBMM_DIST_L2
+    if distance in ("l1", "manhattan"):
+        raise NotImplementedError("distance='l1' is not implemented (no tensor-core form); use 'inner' or 'l2'")
+    raise ValueError("Unrecognized distance type")
 
 _c_ll = ctypes.c_longlong
 _c_int = ctypes.c_int
@@ -40,16 +55,16 @@ SIGNATURES = {
     "fbmm_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ll, _c_ll, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_mbmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int,
                                                       _c_int, _c_int, _c_int, _c_int]),
-    "fbmm_min_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int]),
+    "fbmm_min_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_min_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                                         _c_ptr, _c_size]),
+                                                         _c_int, _c_ptr, _c_size]),
     "fbmm_min_bmm_f32_noalloc": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                                                  _c_int]),
     "fbmm_presplit_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _c_ll,
                                                 _c_ll]),
-    "fbmm_topk_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
+    "fbmm_topk_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_topk_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                                          _c_int, _c_ll, _c_ptr, _c_size]),
+                                                          _c_int, _c_int, _c_ll, _c_ptr, _c_size]),
     "fbmm_topk_merge_f32": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr]),
 }
 

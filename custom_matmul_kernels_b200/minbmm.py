@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .custom_kernel import CustomKernel, check, layout_letter, operand
+from .custom_kernel import CustomKernel, check, distance_code, layout_letter, operand
 
 
 class MinBMMCUDA(CustomKernel):
@@ -13,18 +13,15 @@ class MinBMMCUDA(CustomKernel):
     without ever being written out: dim=1 gives [l,n], dim=2 gives [l,m]
     (minbmm.py:116-121); for 2-D inputs `dim` is bumped by one first (minbmm.py:86-90).
     values are fp32, indices int64. Ties resolve to the lowest index (the reference is
-    racy there, kernels/minbmm.cu:76-79). Only distance="inner" is implemented."""
+    racy there, kernels/minbmm.cu:76-79). distance="inner" reduces the products,
+    distance="l2"/"euclidean" the squared distances sum_k (A[m,k] - B[k,n])^2
+    (minbmm.py:12-19); "l1" is not implemented."""
 
     def __init__(self, patch_m=4, patch_n=4, distance="inner"):
         super().__init__()
         self.patch_m = patch_m
         self.patch_n = patch_n
-        if distance == "inner":
-            pass
-        elif distance in ("l2", "euclidean", "l1", "manhattan"):
-            raise NotImplementedError(f"distance={distance!r} is not implemented; only 'inner' is")
-        else:
-            raise ValueError("Unrecognized distance type")  # minbmm.py:19 builds this but never raises it
+        self._distance_code = distance_code(distance)
         self.distance = distance
 
     def get_mode(self, A, B):
@@ -52,7 +49,7 @@ class MinBMMCUDA(CustomKernel):
         a_keep, a_t, lda, sa = operand(A3)
         b_keep, b_t, ldb, sb = operand(B3)
         # own scratch (packed keys) plus, for large problems, room for pre-split lo planes
-        ws_bytes = (self.lib.fbmm_min_bmm_workspace_bytes(l, m, n, k, dim) + 255) // 256 * 256
+        ws_bytes = (self.lib.fbmm_min_bmm_workspace_bytes(l, m, n, k, dim, self._distance_code) + 255) // 256 * 256
         ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, k, layout_letter(a_t, False), lda, sa,
                                                            layout_letter(b_t, True), ldb, sb)
         ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
@@ -61,7 +58,7 @@ class MinBMMCUDA(CustomKernel):
                 self.stream_ptr(A3.device),
                 a_keep.data_ptr(), layout_letter(a_t, False), lda, sa,
                 b_keep.data_ptr(), layout_letter(b_t, True), ldb, sb,
-                values.data_ptr(), indices.data_ptr(), l, m, n, k, dim,
+                values.data_ptr(), indices.data_ptr(), l, m, n, k, dim, self._distance_code,
                 ws.data_ptr(), ws_bytes))
         if two_d:
             return values[0], indices[0]

@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .custom_kernel import CustomKernel, check, layout_letter, operand
+from .custom_kernel import CustomKernel, check, distance_code, layout_letter, operand
 
 
 class TopkBMMCUDA(CustomKernel):
@@ -14,18 +14,15 @@ class TopkBMMCUDA(CustomKernel):
     gives [l,m,k] (topkbmm.py:119-127) -- not torch.topk's layout for dim=1. 0 < k <= 128
     (topkbmm.py:104). Outputs are contiguous (the reference returns [:,:,:k] views of
     128-wide buffers, topkbmm.py:150-151). Any m and n are handled; where fewer than k
-    entries exist the tail is -inf / -1. Only distance="inner" is implemented."""
+    entries exist the tail is -inf / -1. distance="l2" ranks the squared distances
+    sum_k (A[m,k] - B[k,n])^2 (largest first, as the reference does, topkbmm.py:17-18); "l1"
+    is not implemented."""
 
     def __init__(self, patch_m=4, patch_n=4, distance="inner"):
         super().__init__()
         self.patch_m = patch_m
         self.patch_n = patch_n
-        if distance == "inner":
-            pass
-        elif distance in ("l2", "euclidean", "l1", "manhattan"):
-            raise NotImplementedError(f"distance={distance!r} is not implemented; only 'inner' is")
-        else:
-            raise ValueError("Unrecognized distance type")
+        self._distance_code = distance_code(distance)
         self.distance = distance
 
     def get_mode(self, A, B):
@@ -56,7 +53,7 @@ class TopkBMMCUDA(CustomKernel):
         b_keep, b_t, ldb, sb = operand(B3)
         with torch.cuda.device(A3.device):
             # own scratch (per-chunk lists) plus, for large problems, room for pre-split lo planes
-            ws_bytes = (self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim) + 255) // 256 * 256
+            ws_bytes = (self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim, self._distance_code) + 255) // 256 * 256
             ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, d, layout_letter(a_t, False), lda, sa,
                                                                layout_letter(b_t, True), ldb, sb)
             ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
@@ -64,7 +61,7 @@ class TopkBMMCUDA(CustomKernel):
                 self.stream_ptr(A3.device),
                 a_keep.data_ptr(), layout_letter(a_t, False), lda, sa,
                 b_keep.data_ptr(), layout_letter(b_t, True), ldb, sb,
-                values.data_ptr(), indices.data_ptr(), l, m, n, d, k, dim, index_offset,
+                values.data_ptr(), indices.data_ptr(), l, m, n, d, k, dim, self._distance_code, index_offset,
                 ws.data_ptr(), ws_bytes))
         if two_d:
             return values[0], indices[0]

@@ -39,6 +39,13 @@ extern "C" {
 #define FBMM_ERR_DEVICE (-5)      /* a kernel reported a bounded wait that ran out */
 #define FBMM_ERR_UNSUPPORTED (-6) /* not an sm_100 device */
 
+/* `distance` of min_bmm / topk_bmm, the reference's accumulate functions
+ * (minbmm.py:12-19, kernels/bmm_helpers.cu:20-35): inner product (madd) or squared
+ * Euclidean distance sum_k (a - b)^2 (squared_l2), computed on the tensor cores as
+ * |a|^2 + |b|^2 - 2 a.b. The l1 variants have no matrix-product form and are not built. */
+#define FBMM_DIST_INNER 0
+#define FBMM_DIST_L2 1
+
 /* Library version (major * 1000 + minor). No reference counterpart. */
 int fbmm_version(void);
 
@@ -81,13 +88,14 @@ int fbmm_mbmm_f32(void* stream,
  * (kernels/minbmm.cu:348,252,156,443) with their epilogues min_dim_2 / min_dim_1
  * (kernels/minbmm.cu:86,13), launched from MinBMMCUDA.__call__ (minbmm.py:78-143).
  * `dim` counts on the 3-D product as in minbmm.py:100,116-121. Ties: lowest index.
- * values fp32, indices int64; neither needs initialising. */
-size_t fbmm_min_bmm_workspace_bytes(int l, int m, int n, int k, int dim);
+ * values fp32, indices int64; neither needs initialising. With FBMM_DIST_L2 the reduced
+ * quantity is the squared distance between row m of A and column n of B. */
+size_t fbmm_min_bmm_workspace_bytes(int l, int m, int n, int k, int dim, int distance);
 int fbmm_min_bmm_f32(void* stream,
                      const float* A, int a_layout, long long lda, long long stride_a,
                      const float* B, int b_layout, long long ldb, long long stride_b,
                      float* values, long long* indices,
-                     int l, int m, int n, int k, int dim,
+                     int l, int m, int n, int k, int dim, int distance,
                      void* workspace, size_t workspace_bytes);
 
 /* min_bmm for callers that cannot allocate device memory and cannot supply scratch: a
@@ -132,12 +140,12 @@ size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k,
  * returns [:, :, :k] views of 128-wide buffers, topkbmm.py:150-151). If fewer than topk
  * entries exist the tail is -inf / -1 (kernels/topkbmm.cu:277-278). `index_offset` is
  * added to every index written (used when B holds a column shard). */
-size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim);
+size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim, int distance);
 int fbmm_topk_bmm_f32(void* stream,
                       const float* A, int a_layout, long long lda, long long stride_a,
                       const float* B, int b_layout, long long ldb, long long stride_b,
                       float* values, long long* indices,
-                      int l, int m, int n, int k, int topk, int dim,
+                      int l, int m, int n, int k, int topk, int dim, int distance,
                       long long index_offset,
                       void* workspace, size_t workspace_bytes);
 

@@ -50,23 +50,23 @@ def mbmm(A, B, block_mask, thread_mask, element_mask, share_mask=False):
     return torch.from_numpy(c)
 
 
-def min_bmm(A, B, dim):
+def min_bmm(A, B, dim, distance="inner"):
     a, b = _f(A), _f(B)
     l, m, k = a.shape
     n = b.shape[2]
     r = m if dim == 2 else n
     v = np.empty((l, r), np.float32)
     i = np.empty((l, r), np.int64)
-    _lib().oracle_min_bmm(_p(a), _p(b), _p(v), _p(i), l, m, n, k, dim)
+    _lib().oracle_min_bmm(_p(a), _p(b), _p(v), _p(i), l, m, n, k, dim, int(distance != "inner"))
     return torch.from_numpy(v), torch.from_numpy(i)
 
 
-def topk_bmm(A, B, topk, dim):
+def topk_bmm(A, B, topk, dim, distance="inner"):
     a, b = _f(A), _f(B)
     l, m, k = a.shape
     n = b.shape[2]
     r = m if dim == 2 else n
     v = np.empty((l, r, topk), np.float32)
     i = np.empty((l, r, topk), np.int64)
-    _lib().oracle_topk_bmm(_p(a), _p(b), _p(v), _p(i), l, m, n, k, topk, dim)
+    _lib().oracle_topk_bmm(_p(a), _p(b), _p(v), _p(i), l, m, n, k, topk, dim, int(distance != "inner"))
     return torch.from_numpy(v), torch.from_numpy(i)

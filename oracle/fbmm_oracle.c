@@ -30,6 +30,20 @@ static float dot_fma(const float* a, const float* b, int K, long long ldb) {
   return acc;
 }
 
+/* squared_l2 (kernels/bmm_helpers.cu:28-35): dif = a - b; c = fmaf(dif, dif, c). */
+static float dist_l2(const float* a, const float* b, int K, long long ldb) {
+  float acc = 0.0f;
+  for (int k = 0; k < K; ++k) {
+    const float dif = a[k] - b[(long long)k * ldb];
+    acc = fmaf(dif, dif, acc);
+  }
+  return acc;
+}
+
+static float entry(const float* a, const float* b, int K, long long ldb, int l2) {
+  return l2 ? dist_l2(a, b, K, ldb) : dot_fma(a, b, K, ldb);
+}
+
 void oracle_bmm(const float* A, const float* B, float* C, int L, int M, int N, int K) {
   for (int l = 0; l < L; ++l)
     for (int m = 0; m < M; ++m)
@@ -59,7 +73,7 @@ void oracle_mbmm(const float* A, const float* B, float* C, const uint8_t* block_
 
 /* dim == 2: one result per row m (min over n); dim == 1: one result per column n. */
 void oracle_min_bmm(const float* A, const float* B, float* values, long long* indices, int L, int M, int N, int K,
-                    int dim) {
+                    int dim, int l2) {
   for (int l = 0; l < L; ++l) {
     const int R = dim == 2 ? M : N, S = dim == 2 ? N : M;
     for (int r = 0; r < R; ++r) {
@@ -67,7 +81,7 @@ void oracle_min_bmm(const float* A, const float* B, float* values, long long* in
       long long best_i = 0;
       for (int s = 0; s < S; ++s) {
         const int m = dim == 2 ? r : s, n = dim == 2 ? s : r;
-        const float c = dot_fma(A + ((long long)l * M + m) * K, B + (long long)l * K * N + n, K, N);
+        const float c = entry(A + ((long long)l * M + m) * K, B + (long long)l * K * N + n, K, N, l2);
         if (c < best) { best = c; best_i = s; }
       }
       values[(long long)l * R + r] = best;
@@ -78,7 +92,7 @@ void oracle_min_bmm(const float* A, const float* B, float* values, long long* in
 
 /* Output [l][R][topk], descending; ties keep the lower index first. */
 void oracle_topk_bmm(const float* A, const float* B, float* values, long long* indices, int L, int M, int N, int K,
-                     int topk, int dim) {
+                     int topk, int dim, int l2) {
   for (int l = 0; l < L; ++l) {
     const int R = dim == 2 ? M : N, S = dim == 2 ? N : M;
     for (int r = 0; r < R; ++r) {
@@ -87,7 +101,7 @@ void oracle_topk_bmm(const float* A, const float* B, float* values, long long* i
       int cnt = 0;
       for (int s = 0; s < S; ++s) {
         const int m = dim == 2 ? r : s, n = dim == 2 ? s : r;
-        const float c = dot_fma(A + ((long long)l * M + m) * K, B + (long long)l * K * N + n, K, N);
+        const float c = entry(A + ((long long)l * M + m) * K, B + (long long)l * K * N + n, K, N, l2);
         int pos = cnt;
         while (pos > 0 && v[pos - 1] < c) --pos;      /* strict: earlier index stays ahead on ties */
         if (pos >= topk) continue;

@@ -112,29 +112,47 @@ def mbmm(A, B, block_mask, thread_mask, element_mask, share_mask=False, dtype=to
     return C[0] if two_d else C
 
 
-def min_bmm(A, B, dim=1, dtype=torch.float32):
+def product(A3, B3, distance="inner", dtype=torch.float32):
+    """The [l,m,n] matrix the epilogues reduce: the products (madd,
+    kernels/bmm_helpers.cu:20-26) or, for distance "l2"/"euclidean", the squared distances
+    sum_k (A[m,k] - B[k,n])^2 (squared_l2, kernels/bmm_helpers.cu:28-35; selected in
+    minbmm.py:14-15 and topkbmm.py:17-18), computed directly, not through norms."""
+    A3, B3 = A3.to(dtype), B3.to(dtype)
+    if distance == "inner":
+        return torch.bmm(A3, B3)
+    if distance in ("l2", "euclidean"):
+        out = torch.empty(A3.shape[0], A3.shape[1], B3.shape[2], dtype=dtype)
+        step = max(1, (1 << 24) // max(1, A3.shape[2] * B3.shape[2]))  # bound the broadcast temporary
+        Bt = B3.transpose(1, 2)  # [l, n, k]
+        for r0 in range(0, A3.shape[1], step):
+            d = A3[:, r0:r0 + step, None, :] - Bt[:, None, :, :]
+            out[:, r0:r0 + step] = (d * d).sum(-1)
+        return out
+    raise ValueError(f"distance {distance!r} is not restated")
+
+
+def min_bmm(A, B, dim=1, dtype=torch.float32, distance="inner"):
     """colab/test_minbmm.ipynb:2131-2132; dim counted on the 3-D product, 2-D inputs bump
     dim by one first (minbmm.py:86-90). Returns (values fp32-ish, indices int64)."""
     A3, B3, two_d = _as3d(A, B)
     if two_d:
         dim += 1
     assert dim in (1, 2)
-    C = torch.bmm(A3.to(dtype), B3.to(dtype))
+    C = product(A3, B3, distance, dtype)
     v, i = C.min(dim=dim)
     return (v[0], i[0]) if two_d else (v, i)
 
 
-def topk_bmm(A, B, k=128, dim=1, dtype=torch.float32):
+def topk_bmm(A, B, k=128, dim=1, dtype=torch.float32, distance="inner"):
     """colab/test_topkbmm.ipynb:2673-2677; output [l, R, k] with R = n (dim 1) or m (dim 2),
     largest first (topkbmm.py:119-127, kernels/topkbmm.cu:170-176)."""
     A3, B3, two_d = _as3d(A, B)
     if two_d:
         dim += 1
     assert dim in (1, 2)
-    if dim == 2:
-        C = torch.bmm(A3.to(dtype), B3.to(dtype))
-    else:
-        C = torch.bmm(B3.transpose(1, 2).to(dtype), A3.transpose(1, 2).to(dtype))
+    C = product(A3, B3, distance, dtype)
+    if dim == 1:
+        C = C.transpose(1, 2)
     kk = min(k, C.shape[-1])
     v, i = C.topk(kk, dim=-1)
     if kk < k:  # fewer candidates than k: pad -inf / -1 (kernels/topkbmm.cu:277-278)
@@ -159,13 +177,13 @@ def values_close(got, want, rtol=RTOL, atol=ATOL):
     return bool(ok.all()), float(torch.where(both_inf, torch.zeros_like(err), err).max()) if err.numel() else 0.0
 
 
-def check_min(got_v, got_i, A, B, dim, rtol=RTOL, atol=ATOL):
+def check_min(got_v, got_i, A, B, dim, rtol=RTOL, atol=ATOL, distance="inner"):
     """Values within tolerance of the oracle; each returned index must point at an entry of
     the oracle product that is within tolerance of the oracle minimum. Returns a dict of
     counts; raises AssertionError on failure."""
     A3, B3, two_d = _as3d(A.cpu(), B.cpu())
     d = dim + 1 if two_d else dim
-    C = torch.bmm(A3.double(), B3.double())
+    C = product(A3, B3, distance, torch.float64)
     wv, wi = C.min(dim=d)
     gv = (got_v[None] if two_d else got_v).cpu().double()
     gi = (got_i[None] if two_d else got_i).cpu()
@@ -180,15 +198,14 @@ def check_min(got_v, got_i, A, B, dim, rtol=RTOL, atol=ATOL):
     return {"max_val_err": float(verr.max()), "idx_mismatch": int((gi != wi).sum())}
 
 
-def check_topk(got_v, got_i, A, B, k, dim, rtol=RTOL, atol=ATOL):
+def check_topk(got_v, got_i, A, B, k, dim, rtol=RTOL, atol=ATOL, distance="inner"):
     """Values (descending) within tolerance of the oracle's; every index in range, unique per
     row, and pointing at a product entry within tolerance of the value reported for it."""
     A3, B3, two_d = _as3d(A.cpu(), B.cpu())
     d = dim + 1 if two_d else dim
-    if d == 2:
-        C = torch.bmm(A3.double(), B3.double())
-    else:
-        C = torch.bmm(B3.transpose(1, 2).double(), A3.transpose(1, 2).double())
+    C = product(A3, B3, distance, torch.float64)
+    if d == 1:
+        C = C.transpose(1, 2).contiguous()
     kk = min(k, C.shape[-1])
     wv, wi = C.topk(kk, dim=-1)
     gv = (got_v[None] if two_d else got_v).cpu().double()

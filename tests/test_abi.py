@@ -59,23 +59,27 @@ def test_argument_validation_needs_no_device(lib):
 
 
 def test_topk_and_min_validation(lib):
-    rc = lib.fbmm_topk_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 129, 2, 0, None, 0)
+    rc = lib.fbmm_topk_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 129, 2, 0, 0, None, 0)
     assert rc == ck.FBMM_ERR_INVALID and b"1..128" in lib.fbmm_last_error()
-    rc = lib.fbmm_topk_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 8, 3, 0, None, 0)
+    rc = lib.fbmm_topk_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 8, 3, 0, 0, None, 0)
     assert rc == ck.FBMM_ERR_INVALID and b"dim" in lib.fbmm_last_error()
-    rc = lib.fbmm_min_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 2, None, 0)
+    rc = lib.fbmm_min_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 2, 0, None, 0)
     assert rc == ck.FBMM_ERR_WORKSPACE
+    rc = lib.fbmm_min_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 2, 7, None, 0)
+    assert rc == ck.FBMM_ERR_INVALID and b"distance" in lib.fbmm_last_error()
     rc = lib.fbmm_topk_merge_f32(None, 64, 64, 0, 4, 8, 64, 64)
     assert rc == ck.FBMM_ERR_INVALID
 
 
 def test_workspace_queries(lib):
-    assert lib.fbmm_min_bmm_workspace_bytes(1, 16384, 16384, 64, 2) == 16384 * 8
-    assert lib.fbmm_min_bmm_workspace_bytes(2, 100, 300, 64, 1) == 2 * 300 * 8
+    assert lib.fbmm_min_bmm_workspace_bytes(1, 16384, 16384, 64, 2, 0) == 16384 * 8
+    assert lib.fbmm_min_bmm_workspace_bytes(2, 100, 300, 64, 1, 0) == 2 * 300 * 8
+    # l2 distance adds room for the squared norms of both operands
+    assert lib.fbmm_min_bmm_workspace_bytes(1, 256, 512, 64, 2, 1) == 256 * 8 + 256 * 4 + 512 * 4
     # many row blocks: one column chunk, lists live in the outputs, no scratch
-    assert lib.fbmm_topk_bmm_workspace_bytes(1, 1 << 20, 1 << 20, 256, 64, 2) == 0
+    assert lib.fbmm_topk_bmm_workspace_bytes(1, 1 << 20, 1 << 20, 256, 64, 2, 0) == 0
     # few row blocks: per-chunk candidate lists
-    assert lib.fbmm_topk_bmm_workspace_bytes(1, 128, 1 << 16, 64, 64, 2) > 0
+    assert lib.fbmm_topk_bmm_workspace_bytes(1, 128, 1 << 16, 64, 64, 2, 0) > 0
 
 
 def test_wrappers_reject_bad_inputs_on_cpu():
@@ -91,7 +95,8 @@ def test_wrappers_reject_bad_inputs_on_cpu():
         with pytest.raises(ValueError):
             op(A[0], B)
     with pytest.raises(NotImplementedError):
-        MinBMMCUDA(distance="l2")
+        MinBMMCUDA(distance="l1")
+    assert MinBMMCUDA(distance="euclidean")._distance_code == 1 and TopkBMMCUDA(distance="l2")._distance_code == 1
     with pytest.raises(ValueError):
         TopkBMMCUDA(distance="cosine")
     assert BMMCUDA().get_mode(A, B.transpose(1, 2).contiguous().transpose(1, 2)) == "nt"

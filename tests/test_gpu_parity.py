@@ -276,7 +276,7 @@ def test_c_abi_min_workspace_too_small(dev, lib):
     i = torch.empty(1, 128, device=dev, dtype=torch.int64)
     ws = torch.empty(64, device=dev, dtype=torch.uint8)
     rc = lib.fbmm_min_bmm_f32(None, A.data_ptr(), ord("n"), 32, 0, B.data_ptr(), ord("n"), 128, 0, v.data_ptr(),
-                              i.data_ptr(), 1, 128, 128, 32, 2, ws.data_ptr(), 64)
+                              i.data_ptr(), 1, 128, 128, 32, 2, 0, ws.data_ptr(), 64)
     assert rc == ck.FBMM_ERR_WORKSPACE
 
 
@@ -293,21 +293,21 @@ def test_presplit_scratch_gives_identical_bits(dev, lib):
         assert extra >= (m * k + k * n) * 4
         outs = []
         for use_extra in (False, True):
-            own = (lib.fbmm_min_bmm_workspace_bytes(1, m, n, k, 2) + 255) // 256 * 256
+            own = (lib.fbmm_min_bmm_workspace_bytes(1, m, n, k, 2, 0) + 255) // 256 * 256
             nbytes = own + (extra if use_extra else 0)
             ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
             v = torch.empty(1, m, device=dev)
             i = torch.empty(1, m, device=dev, dtype=torch.int64)
             rc = lib.fbmm_min_bmm_f32(stream, A.data_ptr(), ord("n"), k, m * k, B.data_ptr(), ord("n"), n, k * n,
-                                      v.data_ptr(), i.data_ptr(), 1, m, n, k, 2, ws.data_ptr(), nbytes)
+                                      v.data_ptr(), i.data_ptr(), 1, m, n, k, 2, 0, ws.data_ptr(), nbytes)
             assert rc == 0, lib.fbmm_last_error()
-            own_t = (lib.fbmm_topk_bmm_workspace_bytes(1, m, n, k, 16, 2) + 255) // 256 * 256
+            own_t = (lib.fbmm_topk_bmm_workspace_bytes(1, m, n, k, 16, 2, 0) + 255) // 256 * 256
             nb_t = own_t + (extra if use_extra else 0)
             ws_t = torch.empty(max(nb_t, 256), device=dev, dtype=torch.uint8)
             tv = torch.empty(1, m, 16, device=dev)
             ti = torch.empty(1, m, 16, device=dev, dtype=torch.int64)
             rc = lib.fbmm_topk_bmm_f32(stream, A.data_ptr(), ord("n"), k, m * k, B.data_ptr(), ord("n"), n, k * n,
-                                       tv.data_ptr(), ti.data_ptr(), 1, m, n, k, 16, 2, 0, ws_t.data_ptr(), nb_t)
+                                       tv.data_ptr(), ti.data_ptr(), 1, m, n, k, 16, 2, 0, 0, ws_t.data_ptr(), nb_t)
             assert rc == 0, lib.fbmm_last_error()
             torch.cuda.synchronize()
             outs.append((v, i, tv, ti))
@@ -317,3 +317,36 @@ def test_presplit_scratch_gives_identical_bits(dev, lib):
         R.check_topk(outs[1][2], outs[1][3], A.cpu(), B.cpu(), 16, 2)
     assert lib.fbmm_presplit_workspace_bytes(1, 512, 4096, 64, ord("n"), 64, 0, ord("n"), 4096, 0) == 0
     assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
+
+
+# ----------------------------------------------------------------------------- l2 distance
+@pytest.mark.parametrize("shape", [(1, 200, 40, 300), (2, 130, 64, 257), (1, 1100, 96, 1300), (1, 64, 200, 520)])
+def test_min_and_topk_l2_distance(dev, lib, shape):
+    """distance="l2": squared distances sum_k (a - b)^2 (squared_l2 of the reference), both
+    dims, all four layouts for one shape; checked against the direct fp64 formula."""
+    from custom_matmul_kernels_b200 import MinBMMCUDA, TopkBMMCUDA
+    l, m, k, n = shape
+    g = torch.Generator().manual_seed(sum(shape) + 1)
+    A, B = torch.randn(l, m, k, generator=g), torch.randn(l, k, n, generator=g)
+    mn, tk = MinBMMCUDA(distance="l2"), TopkBMMCUDA(distance="euclidean")
+    combos = layouts(A.to(dev), B.to(dev)) if shape[1] == 200 else {"nn": (A.to(dev), B.to(dev))}
+    for mode, (a, b) in combos.items():
+        for dim in (1, 2):
+            v, i = mn(a, b, dim=dim)
+            R.check_min(v, i, A, B, dim, distance="l2")
+            tv, ti = tk(a, b, k=9, dim=dim)
+            R.check_topk(tv, ti, A, B, 9, dim, distance="l2")
+    device_ok(lib)
+
+
+def test_l2_distance_exact_and_nonnegative(dev, lib):
+    """Integer operands: every squared distance is an exact integer, so values must match
+    the oracle bit for bit; a column of B equal to a row of A gives distance exactly 0."""
+    from custom_matmul_kernels_b200 import MinBMMCUDA
+    A, B = R.exact_inputs(1, 140, 24, 300, seed=41, lo=-4, hi=4)
+    B[0, :, 17] = A[0, 5]
+    v, i = MinBMMCUDA(distance="l2")(A.to(dev), B.to(dev), dim=2)
+    wv, wi = R.min_bmm(A, B, dim=2, distance="l2")
+    assert torch.equal(v.cpu(), wv) and torch.equal(i.cpu(), wi)
+    assert float(v[0, 5]) == 0.0 and bool((v >= 0).all())
+    device_ok(lib)

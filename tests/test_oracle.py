@@ -166,3 +166,20 @@ def test_config_generators_are_seeded_and_shaped():
     c2 = R.make_inputs("c2", batches=1, rows=8, cols=8)
     assert float(c2["A"].abs().max()) <= 1.0
     assert R.flops(*R.CONFIG_SHAPES["c1"]) == 2.0 * 16384 * 16384 * 64
+
+
+def test_l2_distance_restatements_agree():
+    """squared_l2 (kernels/bmm_helpers.cu:28-35): the torch restatement (direct formula) and
+    the C restatement (fmaf chain) agree, and both equal |a|^2 + |b|^2 - 2 a.b in fp64."""
+    A, B = R.exact_inputs(2, 20, 6, 30, seed=8, lo=-3, hi=3)
+    D = R.product(A, B, "l2")
+    ref = (A.double() ** 2).sum(-1)[:, :, None] + (B.double() ** 2).sum(1)[:, None, :] - 2 * torch.bmm(A.double(), B.double())
+    assert torch.equal(D.double(), ref)
+    for dim in (1, 2):
+        v, i = R.min_bmm(A, B, dim=dim, distance="l2")
+        cv, ci = CO.min_bmm(A, B, dim, distance="l2")
+        assert torch.equal(v, cv) and torch.equal(i, ci)
+        tv, _ = R.topk_bmm(A, B, k=4, dim=dim, distance="l2")
+        ctv, cti = CO.topk_bmm(A, B, 4, dim, distance="l2")
+        assert torch.equal(tv, ctv)
+        R.check_topk(ctv, cti, A, B, 4, dim, distance="l2")

@@ -29,9 +29,9 @@ def _call_pair(lib, A, B, dim):
         if noalloc:
             rc = lib.fbmm_min_bmm_f32_noalloc(*common)
         else:
-            nbytes = lib.fbmm_min_bmm_workspace_bytes(l, m, n, k, dim)
+            nbytes = lib.fbmm_min_bmm_workspace_bytes(l, m, n, k, dim, 0)
             ws = torch.empty(nbytes, device=A.device, dtype=torch.uint8)
-            rc = lib.fbmm_min_bmm_f32(*common, ws.data_ptr(), nbytes)
+            rc = lib.fbmm_min_bmm_f32(*common, 0, ws.data_ptr(), nbytes)
         assert rc == 0, lib.fbmm_last_error()
         out.append((v, i))
     torch.cuda.synchronize()
