@@ -184,7 +184,7 @@ class Workload:
             l_, m_, k_ = self.A.shape
             n_ = self.B.shape[2]
             if self.op.lib.fbmm_presplit_workspace_bytes(l_, m_, n_, k_, ord("n"), k_, m_ * k_, ord("n"), n_, k_ * n_):
-                self.kernels_per_step += 2  # one lo-plane pass per operand
+                self.kernels_per_step += 1  # lo-plane pass over B (A is split in shared memory)
         else:
             self.op = TopkBMMCUDA()
             self.kernels_per_step = 1 + (1 if world > 1 else 0)  # + candidate merge

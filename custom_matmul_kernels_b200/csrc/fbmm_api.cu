@@ -257,9 +257,13 @@ bool presplit_worthwhile(const RowProblem& p) {
   return operand_span(p.a, p.K, p.L) <= 2 * dense_a && operand_span(p.b, p.K, p.L) <= 2 * dense_b;
 }
 
+bool a_stays_resident(int k) { return (k + kKBlock - 1) / kKBlock <= kMaxResidentKBlocks; }
+
+// Room for the lo planes: the column operand always, the row operand only when it streams
+// through the ring (K > 128); a resident row block is split in shared memory.
 size_t presplit_bytes(const RowProblem& p) {
-  return align_up(static_cast<size_t>(operand_span(p.a, p.K, p.L)) * 4, 256) +
-         align_up(static_cast<size_t>(operand_span(p.b, p.K, p.L)) * 4, 256);
+  const size_t a = a_stays_resident(p.K) ? 0 : align_up(static_cast<size_t>(operand_span(p.a, p.K, p.L)) * 4, 256);
+  return a + align_up(static_cast<size_t>(operand_span(p.b, p.K, p.L)) * 4, 256);
 }
 
 size_t norms_bytes(const RowProblem& p) {
@@ -306,18 +310,23 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
   if ((rc = make_tensor_map(&tb, p.b, p.K, p.L, kTileN)) != FBMM_OK) return rc;
   const bool presplit = lo_scratch != nullptr && (EPI == kEpiMin || EPI == kEpiTopk);
   if (presplit) {
+    const bool a_too = !a_stays_resident(p.K);
     const long long span_a = operand_span(p.a, p.K, p.L), span_b = operand_span(p.b, p.K, p.L);
     float* a_lo = static_cast<float*>(lo_scratch);
-    float* b_lo = reinterpret_cast<float*>(static_cast<char*>(lo_scratch) + align_up(static_cast<size_t>(span_a) * 4, 256));
+    float* b_lo = a_too ? reinterpret_cast<float*>(static_cast<char*>(lo_scratch) + align_up(static_cast<size_t>(span_a) * 4, 256))
+                        : static_cast<float*>(lo_scratch);
     const int threads = 256;
     const int blocks = st.sms * 8;
-    fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.a.ptr, a_lo, span_a);
+    if (a_too) fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.a.ptr, a_lo, span_a);
     fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.b.ptr, b_lo, span_b);
     FBMM_CUDA(cudaGetLastError());
     Operand oa = p.a, ob = p.b;
-    oa.ptr = a_lo;
     ob.ptr = b_lo;
-    if ((rc = make_tensor_map(&ta_lo, oa, p.K, p.L, kTileM)) != FBMM_OK) return rc;
+    ta_lo = ta;
+    if (a_too) {
+      oa.ptr = a_lo;
+      if ((rc = make_tensor_map(&ta_lo, oa, p.K, p.L, kTileM)) != FBMM_OK) return rc;
+    }
     if ((rc = make_tensor_map(&tb_lo, ob, p.K, p.L, kTileN)) != FBMM_OK) return rc;
   } else {
     ta_lo = ta;
@@ -326,7 +335,7 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
   const long long grid = shape.num_units < st.sms ? shape.num_units : st.sms;
   const int kblocks = (p.K + kKBlock - 1) / kKBlock;
   // Up to K = 128 the row block of A stays in shared memory for the whole unit.
-  const bool a_resident = kblocks <= kMaxResidentKBlocks;
+  const bool a_resident = a_stays_resident(p.K);
   const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk);
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
   const unsigned g = static_cast<unsigned>(grid);

@@ -371,9 +371,10 @@ __device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint
   }
 }
 
-// PRESPLIT: the lo planes of A and B were computed once by fbmm_split_lo_kernel into global
-// scratch with the operands' own strides; TMA then brings hi and lo, the splitter warps
-// stand idle and a ring stage is ready the moment its copies land.
+// PRESPLIT: lo planes were computed once by fbmm_split_lo_kernel into global scratch with
+// the operands' own strides; TMA then brings hi and lo of everything that streams through
+// the ring, and a ring stage is ready the moment its copies land. A resident row block of
+// A is still split in shared memory (once per unit, so there is nothing to save).
 template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -503,9 +504,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               // unit's last tile has finished with that k-block
               ok = mbar_wait(&bars->a_empty[kb], a_phase ^ 1u, abort_flag);
               if (!ok) break;
-              mbar_arrive_expect_tx(&bars->a_full[kb], PRESPLIT ? 2 * kPlaneBytes : kPlaneBytes);
+              mbar_arrive_expect_tx(&bars->a_full[kb], kPlaneBytes);
               load_a(&tmap_a, a_region + kb * 2 * kPlaneBytes + off_a_hi, &bars->a_full[kb], kb, mb, b);
-              if (PRESPLIT) load_a(&tmap_a_lo, a_region + kb * 2 * kPlaneBytes + off_a_lo, &bars->a_full[kb], kb, mb, b);
             }
             FBMM_PROF_BEGIN();
             ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag);
@@ -570,7 +570,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t acc_small = acc_big + TILE_N;
           for (int kb = 0; kb < kblocks; ++kb) {
             if (A_RES && t == first) {
-              ok = mbar_wait(PRESPLIT ? &bars->a_full[kb] : &bars->a_split[kb], a_phase, abort_flag);
+              ok = mbar_wait(&bars->a_split[kb], a_phase, abort_flag);
               if (!ok) break;
             }
             FBMM_PROF_BEGIN();
@@ -605,8 +605,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ hi/lo splitters
-    if (PRESPLIT) {
-      // nothing to split: the lo planes arrive by TMA
+    if (PRESPLIT && !A_RES) {
+      // nothing to split: every lo plane arrives by TMA
     } else {
     const int st = static_cast<int>(threadIdx.x) - 64;
     uint32_t stage = 0, phase = 0, a_phase = 0;
@@ -618,6 +618,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (!live_range(b, mb, t0, t1, first, last)) continue;
       for (int t = first; t <= last && ok; ++t) {
         if (!tile_live(b, mb, t)) continue;
+        if (PRESPLIT && t != first) break;  // only the unit's resident A block needs splitting
         for (int kb = 0; kb < kblocks; ++kb) {
           if (A_RES && t == first) {
             ok = mbar_wait(&bars->a_full[kb], a_phase, abort_flag);
@@ -627,6 +628,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             fence_proxy_async_smem();
             mbar_arrive(&bars->a_split[kb]);
           }
+          if (PRESPLIT) continue;
           FBMM_PROF_BEGIN();
           ok = mbar_wait(&bars->full[stage], phase, abort_flag);
           FBMM_PROF_END(0);

@@ -122,8 +122,9 @@ int fbmm_min_bmm_f32_noalloc(void* stream,
 /* Optional extra scratch for fbmm_min_bmm_f32 and fbmm_topk_bmm_f32. The kernels form every
  * fp32 product from three tf32 products of (hi, lo) operand planes; normally the lo planes
  * are produced in shared memory tile by tile. When the caller's workspace has this many
- * bytes beyond the op's own need (rounded up to 256), the lo planes of A and B are computed
- * once into that room instead, which pays when every tile is fetched many times. Returns 0
+ * bytes beyond the op's own need (rounded up to 256), the lo planes of the operands that
+ * stream through shared memory (the column operand; for k > 128 the row operand too) are
+ * computed once into that room instead, which pays when every tile is fetched many times. Returns 0
  * for shapes where it would not be used (fewer than 1024 rows or columns, or storage with
  * large gaps, or a column operand whose two planes exceed 96 MB and would fall out of L2).
  * Same answers either way. No reference counterpart (its kernels multiply in
