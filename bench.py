@@ -281,14 +281,16 @@ def algorithmic_bytes(name, units):
 
 
 def measured_traffic(name, units):
-    """DRAM bytes per launch from the ncu capture summarised in profiles/ (c4 min kernel with
-    pre-split lo planes at 262 144 rows: 875.0 MB read + 5.7 MB written), scaled by the rows
-    processed: A hi+lo and the outputs grow with the rows, and B (hi+lo 67 MB, just over what
-    L2 keeps between sweeps) is re-read from HBM roughly once per wave of row blocks, which
-    also grows with the rows. None where no capture has been taken."""
+    """DRAM bytes per launch from the ncu capture summarised in profiles/ (c4 min kernel at
+    262 144 rows: 352.3 MB read + 5.4 MB written), scaled by the rows processed: B's hi and lo
+    planes (67.1 MB) are read once per launch whatever the row count; the rest (A, read once
+    per column range = twice, and the outputs) grows with the rows. None where no capture
+    has been taken."""
     if name != "c4":
         return None
-    return units * (875.006208e6 + 5.70624e6) / 262144.0
+    b_planes = 2 * 128 * 65536 * 4
+    per_row = (352.28288e6 + 5.39648e6 - b_planes) / 262144.0
+    return b_planes + units * per_row
 
 
 def cpu_baseline(name):

@@ -494,7 +494,24 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   // room behind the op's own scratch for the lo planes? then the operands are split once up front
   void* lo_scratch = nullptr;
   const size_t lo_off = align_up(need, 256);
-  if (presplit_worthwhile(p) && workspace_bytes >= lo_off + presplit_bytes(p)) lo_scratch = static_cast<char*>(workspace) + lo_off;
+  if (presplit_worthwhile(p) && workspace_bytes >= lo_off + presplit_bytes(p)) {
+    lo_scratch = static_cast<char*>(workspace) + lo_off;
+    // B's two planes should stay in L2 while every row block passes over them. What L2
+    // keeps of data that all SMs share is about half its size, so wider B is swept in
+    // column ranges of at most 40 MB (hi + lo), all row blocks per range; the packed
+    // atomicMin keys make the ranges independent.
+    const long long b_bytes = operand_span(p.b, p.K, p.L) * 8;
+    const long long limit = 40ll * 1024 * 1024;
+    if (b_bytes > limit && p.L == 1) {
+      const int want = static_cast<int>((b_bytes + limit - 1) / limit);
+      if (want > s.n_chunks && want <= s.n_tiles) {
+        s.tiles_per_chunk = (s.n_tiles + want - 1) / want;
+        s.n_chunks = (s.n_tiles + s.tiles_per_chunk - 1) / s.tiles_per_chunk;
+        s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+      }
+      s.chunk_major = 1;
+    }
+  }
   if ((rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e, lo_scratch)) != FBMM_OK) return rc;
   const int threads = 256;
   const long long blocks = (rows + threads - 1) / threads;

@@ -76,6 +76,9 @@ struct GemmShape {
   int n_chunks;         // column chunks per row block
   int tiles_per_chunk;  // column tiles per chunk
   long long num_units;  // L * m_blocks * n_chunks
+  int chunk_major;      // unit order: 0 = chunks of one row block are consecutive,
+                        // 1 = all row blocks of chunk 0 first, then chunk 1, ... (keeps the
+                        // CTAs inside one L2-sized column range of B at a time)
 };
 
 struct EpiArgs {
@@ -440,8 +443,9 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   // Decodes unit u into batch, row block and column-tile range.
   auto decode = [&](long long u, int& b, int& mb, int& t0, int& t1) {
-    const int c = static_cast<int>(u % shape.n_chunks);
-    const long long r = u / shape.n_chunks;
+    const long long row_blocks = static_cast<long long>(shape.L) * shape.m_blocks;
+    const int c = static_cast<int>(shape.chunk_major ? u / row_blocks : u % shape.n_chunks);
+    const long long r = shape.chunk_major ? u % row_blocks : u / shape.n_chunks;
     mb = static_cast<int>(r % shape.m_blocks);
     b = static_cast<int>(r / shape.m_blocks);
     t0 = c * shape.tiles_per_chunk;
