@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -47,17 +48,26 @@ std::mutex g_mu;
 DeviceState g_dev[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
 
+template <int EPI, int E, bool AR, bool PS, bool PR>
+int set_one_attr() {
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, AR, PS, PR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kSmemLimit)));
+  return FBMM_OK;
+}
+
 template <int EPI, int E>
 int set_smem_attr() {
-  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(kSmemLimit)));
-  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(kSmemLimit)));
+  int rc;
+  if ((rc = set_one_attr<EPI, E, false, false, false>()) != FBMM_OK) return rc;
+  if ((rc = set_one_attr<EPI, E, true, false, false>()) != FBMM_OK) return rc;
+  if ((rc = set_one_attr<EPI, E, false, false, true>()) != FBMM_OK) return rc;
+  if ((rc = set_one_attr<EPI, E, true, false, true>()) != FBMM_OK) return rc;
   if (EPI == kEpiMin || EPI == kEpiTopk) {
-    FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   static_cast<int>(kSmemLimit)));
-    FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   static_cast<int>(kSmemLimit)));
+    constexpr bool kPs = (EPI == kEpiMin || EPI == kEpiTopk);
+    if ((rc = set_one_attr<EPI, E, false, kPs, false>()) != FBMM_OK) return rc;
+    if ((rc = set_one_attr<EPI, E, true, kPs, false>()) != FBMM_OK) return rc;
+    if ((rc = set_one_attr<EPI, E, false, kPs, true>()) != FBMM_OK) return rc;
+    if ((rc = set_one_attr<EPI, E, true, kPs, true>()) != FBMM_OK) return rc;
   }
   return FBMM_OK;
 }
@@ -298,6 +308,21 @@ int check_distance(int distance) {
   return FBMM_OK;
 }
 
+// CTA pairs (clusters of two, tcgen05 cta_group::2) work on 256-row blocks; with 128 rows
+// or fewer the second CTA would have nothing to do. The pair kernels give the same results
+// as the single-CTA ones but are not faster yet, so they run only when FBMM_PAIRS=1 is set
+// in the environment (read once per process).
+bool use_pairs(int rows) {
+  static const bool enabled = [] {
+    const char* e = getenv("FBMM_PAIRS");
+    return e != nullptr && e[0] == '1';
+  }();
+  return enabled && rows > kTileM;
+}
+
+// Workers that walk the unit list: SMs, or SM pairs.
+int unit_workers(int sms, int rows) { return use_pairs(rows) ? sms / 2 : sms; }
+
 // Launches the fused kernel. `lo_scratch` (or null) is room for the lo planes of both
 // operands (presplit_bytes): when given, they are computed here by one element-wise pass
 // each and the kernel runs without its splitter stage.
@@ -306,8 +331,10 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
                 void* lo_scratch = nullptr) {
   CUtensorMap ta, tb, ta_lo, tb_lo;
   int rc;
+  const bool pairs = use_pairs(p.M);
+  const int b_box = pairs ? kTileN / 2 : kTileN;  // a CTA of a pair fetches half of each B tile
   if ((rc = make_tensor_map(&ta, p.a, p.K, p.L, kTileM)) != FBMM_OK) return rc;
-  if ((rc = make_tensor_map(&tb, p.b, p.K, p.L, kTileN)) != FBMM_OK) return rc;
+  if ((rc = make_tensor_map(&tb, p.b, p.K, p.L, b_box)) != FBMM_OK) return rc;
   const bool presplit = lo_scratch != nullptr && (EPI == kEpiMin || EPI == kEpiTopk);
   if (presplit) {
     const bool a_too = !a_stays_resident(p.K);
@@ -327,35 +354,43 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
       oa.ptr = a_lo;
       if ((rc = make_tensor_map(&ta_lo, oa, p.K, p.L, kTileM)) != FBMM_OK) return rc;
     }
-    if ((rc = make_tensor_map(&tb_lo, ob, p.K, p.L, kTileN)) != FBMM_OK) return rc;
+    if ((rc = make_tensor_map(&tb_lo, ob, p.K, p.L, b_box)) != FBMM_OK) return rc;
   } else {
     ta_lo = ta;
     tb_lo = tb;
   }
-  const long long grid = shape.num_units < st.sms ? shape.num_units : st.sms;
+  const int workers = unit_workers(st.sms, p.M);
+  const long long active = shape.num_units < workers ? shape.num_units : workers;
   const int kblocks = (p.K + kKBlock - 1) / kKBlock;
   // Up to K = 128 the row block of A stays in shared memory for the whole unit.
   const bool a_resident = a_stays_resident(p.K);
-  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk);
+  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, pairs);
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
-  const unsigned g = static_cast<unsigned>(grid);
-  if (EPI == kEpiMin || EPI == kEpiTopk) {
-    constexpr int EP = (EPI == kEpiMin || EPI == kEpiTopk) ? EPI : kEpiMin;  // keeps the store kernels out of this branch
-    if (presplit && a_resident)
-      fbmm_gemm_kernel<EP, E, true, true><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
-    else if (presplit)
-      fbmm_gemm_kernel<EP, E, false, true><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
-    else if (a_resident)
-      fbmm_gemm_kernel<EP, E, true, false><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
-    else
-      fbmm_gemm_kernel<EP, E, false, false><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
+  // min / top-k have pre-split variants; store / mask never use them
+  constexpr bool kHasPresplit = (EPI == kEpiMin || EPI == kEpiTopk);
+  const bool ps = kHasPresplit && presplit;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(active) * (pairs ? 2u : 1u), 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = plan.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = pairs ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+#define FBMM_LAUNCH(AR, PS, PR) \
+  FBMM_CUDA(cudaLaunchKernelEx(&cfg, fbmm_gemm_kernel<EPI, E, AR, PS, PR>, ta, tb, ta_lo, tb_lo, shape, epi))
+  if (pairs) {
+    if (a_resident) { if (ps) FBMM_LAUNCH(true, kHasPresplit, true); else FBMM_LAUNCH(true, false, true); }
+    else            { if (ps) FBMM_LAUNCH(false, kHasPresplit, true); else FBMM_LAUNCH(false, false, true); }
   } else {
-    if (a_resident)
-      fbmm_gemm_kernel<EPI, E, true, false><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
-    else
-      fbmm_gemm_kernel<EPI, E, false, false><<<g, kNumThreads, plan.total, stream>>>(ta, tb, ta_lo, tb_lo, shape, epi);
+    if (a_resident) { if (ps) FBMM_LAUNCH(true, kHasPresplit, false); else FBMM_LAUNCH(true, false, false); }
+    else            { if (ps) FBMM_LAUNCH(false, kHasPresplit, false); else FBMM_LAUNCH(false, false, false); }
   }
-  FBMM_CUDA(cudaGetLastError());
+#undef FBMM_LAUNCH
   return FBMM_OK;
 }
 
@@ -364,7 +399,8 @@ GemmShape base_shape(const RowProblem& p) {
   s.L = p.L; s.M = p.M; s.N = p.N; s.K = p.K;
   s.a_mn = p.a.mn_major ? 1 : 0;
   s.b_mn = p.b.mn_major ? 1 : 0;
-  s.m_blocks = (p.M + kTileM - 1) / kTileM;
+  const int rows_per_block = use_pairs(p.M) ? 2 * kTileM : kTileM;
+  s.m_blocks = (p.M + rows_per_block - 1) / rows_per_block;
   s.n_tiles = (p.N + kTileN - 1) / kTileN;
   return s;
 }
@@ -415,7 +451,7 @@ int fbmm_bmm_f32(void* stream, const float* A, int a_layout, long long lda, long
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, p.M), kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   EpiArgs e{};
   e.C = C; e.ldc = ldc; e.stride_c = stride_c;
@@ -439,7 +475,7 @@ int fbmm_mbmm_f32(void* stream, const float* A, int a_layout, long long lda, lon
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, p.M), kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   EpiArgs e{};
   e.C = C; e.ldc = ldc; e.stride_c = stride_c;
@@ -481,7 +517,7 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, p.M), kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   const long long rows = static_cast<long long>(l) * p.M;
   unsigned long long* keys = static_cast<unsigned long long*>(workspace);
@@ -532,7 +568,9 @@ size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k, int a_layout, l
 }
 
 static void topk_plan(int l, int rows_per_batch, int cols, int sms, int* n_chunks, int* tiles_per_chunk) {
-  const int m_blocks = (rows_per_batch + kTileM - 1) / kTileM;
+  const int rows_per_block = use_pairs(rows_per_batch) ? 2 * kTileM : kTileM;
+  const int m_blocks = (rows_per_batch + rows_per_block - 1) / rows_per_block;
+  sms = unit_workers(sms, rows_per_batch);
   const int n_tiles = (cols + kTileN - 1) / kTileN;
   choose_chunks(l, m_blocks, n_tiles, sms, kTopkOverheadTiles, kMaxChunks, n_chunks, tiles_per_chunk);
 }
@@ -764,7 +802,7 @@ extern "C" int fbmm_min_bmm_f32_noalloc(void* stream_, const float* A, int a_lay
   unsigned long long* keys = nullptr;
   if ((rc = noalloc_keys_for_current_device(&keys)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, p.M), kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   // The array keeps the previous call's keys: every key this call will reduce into must
   // start at all-ones again.

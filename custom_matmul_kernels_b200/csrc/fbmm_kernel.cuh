@@ -336,10 +336,11 @@ constexpr uint32_t kSmemLimit = 232448;  // 227 KB per CTA on sm_100
 struct SmemPlan {
   uint32_t a_bytes, stage_bytes, stages, epi_bytes, total;
 };
-__host__ __device__ inline SmemPlan make_smem_plan(bool a_resident, int kblocks, bool topk) {
+__host__ __device__ inline SmemPlan make_smem_plan(bool a_resident, int kblocks, bool topk, bool pair) {
   SmemPlan p;
+  const uint32_t b_plane = pair ? kPlaneBytes / 2u : kPlaneBytes;  // a CTA of a pair holds half of each B tile
   p.a_bytes = a_resident ? static_cast<uint32_t>(kblocks) * 2u * kPlaneBytes : 0u;
-  p.stage_bytes = a_resident ? 2u * kPlaneBytes : 4u * kPlaneBytes;
+  p.stage_bytes = (a_resident ? 0u : 2u * kPlaneBytes) + 2u * b_plane;
   p.epi_bytes = topk ? kTopkStageBytes : 0u;
   const uint32_t fixed = p.a_bytes + p.epi_bytes + kBarrierBytes + 1024u /* alignment slack */;
   uint32_t st = (kSmemLimit - fixed) / p.stage_bytes;
@@ -378,7 +379,18 @@ __device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint
 // the operands' own strides; TMA then brings hi and lo of everything that streams through
 // the ring, and a ring stage is ready the moment its copies land. A resident row block of
 // A is still split in shared memory (once per unit, so there is nothing to save).
-template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT>
+//
+// PAIR: the kernel runs as clusters of two CTAs on 256-row blocks. Each CTA loads, splits
+// and keeps its own 128 rows of A and HALF of every B tile (64 columns); the even CTA issues
+// tcgen05.mma.cta_group::2 (M = 256), which reads A and its half of B from each CTA's own
+// shared memory and writes each CTA's 128 accumulator rows into its own TMEM. Per SM that
+// halves the B bytes the tensor core pulls from shared memory and the B bytes TMA writes,
+// and in isolation N = 128 runs at 64 cycles per MMA instead of 88. Barriers that gate the
+// MMAs live in the even CTA (the peer arrives on them through the cluster window); commits
+// release both CTAs' stages. Results are identical to the single-CTA kernels; the whole
+// kernel is currently ~20 % slower than they are (the tensor pipe sits idle between pair
+// MMAs for a reason not yet found), so the library uses pairs only when asked to.
+template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT, bool PAIR>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_a_lo, const __grid_constant__ CUtensorMap tmap_b_lo,
@@ -388,12 +400,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   static_assert(2 * kAccStages * TILE_N <= kTmemCols, "TMEM budget");
 
   const int kblocks = (shape.K + kKBlock - 1) / kKBlock;
-  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk);
+  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, PAIR);
   const uint32_t stages = plan.stages;
+  constexpr uint32_t kBPlane = PAIR ? kPlaneBytes / 2u : kPlaneBytes;  // this CTA's part of a B tile plane
+  constexpr int kBCols = PAIR ? TILE_N / 2 : TILE_N;                  // ... in columns
   // offsets inside a ring stage
   const uint32_t off_a_hi = 0, off_a_lo = kPlaneBytes;
   const uint32_t off_b_hi = A_RES ? 0u : 2u * kPlaneBytes;
-  const uint32_t off_b_lo = off_b_hi + kPlaneBytes;
+  const uint32_t off_b_lo = off_b_hi + kBPlane;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -405,21 +419,27 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const uint32_t warp = threadIdx.x >> 5;
   const uint32_t lane = lane_id();
+  const uint32_t cta_rank = PAIR ? cluster_cta_rank() : 0u;  // 0 = the CTA that issues the MMAs
+  constexpr uint32_t kCtas = PAIR ? 2u : 1u;
+  // the barrier block of both CTAs of a pair in the cluster window
+  const uint32_t bars_cta0 = PAIR ? map_to_cta(smem_u32(bars), 0) : smem_u32(bars);
+  const uint32_t bars_cta1 = PAIR ? map_to_cta(smem_u32(bars), 1) : smem_u32(bars);
+  auto bar_off = [&](const uint64_t* b) -> uint32_t { return smem_u32(b) - smem_u32(bars); };
 
   if (threadIdx.x == 0) {
     bars->abort_flag = 0;
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->split[s], kSplitThreads);
+      mbar_init(&bars->split[s], kSplitThreads * kCtas);
       mbar_init(&bars->empty[s], 1);
     }
     for (int s = 0; s < kAccStages; ++s) {
       mbar_init(&bars->acc_full[s], 1);
-      mbar_init(&bars->acc_empty[s], kEpiThreads);
+      mbar_init(&bars->acc_empty[s], kEpiThreads * kCtas);
     }
     for (int s = 0; s < kMaxResidentKBlocks; ++s) {
       mbar_init(&bars->a_full[s], 1);
-      mbar_init(&bars->a_split[s], kSplitThreads);
+      mbar_init(&bars->a_split[s], kSplitThreads * kCtas);
       mbar_init(&bars->a_empty[s], 1);
     }
     fence_barrier_init();
@@ -431,15 +451,25 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   }
   if (warp == 1) {
-    tmem_alloc(&bars->tmem_base, kTmemCols);
-    tmem_relinquish_alloc_permit();
+    if (PAIR) {
+      tmem_alloc_pair(&bars->tmem_base, kTmemCols);
+      tmem_relinquish_alloc_permit_pair();
+    } else {
+      tmem_alloc(&bars->tmem_base, kTmemCols);
+      tmem_relinquish_alloc_permit();
+    }
   }
   tcgen05_fence_before_sync();
-  __syncthreads();
+  if (PAIR) cluster_sync_all(); else __syncthreads();
   tcgen05_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
 
   const long long units = shape.num_units;
+  // a pair walks the unit list as one worker
+  const long long unit_first = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+  const long long unit_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
+  // first row of this CTA inside row block `mb` (row blocks are 256 rows for pairs)
+  auto row_base = [&](int mb) -> int { return PAIR ? mb * 2 * kTileM + static_cast<int>(cta_rank) * kTileM : mb * kTileM; };
 
   // Decodes unit u into batch, row block and column-tile range.
   auto decode = [&](long long u, int& b, int& mb, int& t0, int& t1) {
@@ -453,9 +483,19 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   };
   // Block-mask test of the mask epilogue (kernels/mbmm.cu:251-255): a zero byte means
   // the 128x128 tile is neither loaded nor multiplied.
+  auto block_live = [&](int b, int mb128, int t) -> bool {
+    if (mb128 * kTileM >= shape.M) return false;
+    return epi.block_mask[b * epi.bm_stride + static_cast<long long>(mb128) * epi.bm_cols + t] != 0;
+  };
+  // this CTA's own 128x128 block
+  auto tile_live_own = [&](int b, int mb, int t) -> bool {
+    if (EPI != kEpiMask) return true;
+    return block_live(b, PAIR ? mb * 2 + static_cast<int>(cta_rank) : mb, t);
+  };
+  // the tile as the loads and MMAs see it: for a pair, live when either block is
   auto tile_live = [&](int b, int mb, int t) -> bool {
     if (EPI != kEpiMask) return true;
-    return epi.block_mask[b * epi.bm_stride + static_cast<long long>(mb) * epi.bm_cols + t] != 0;
+    return PAIR ? (block_live(b, mb * 2, t) || block_live(b, mb * 2 + 1, t)) : block_live(b, mb, t);
   };
   // First and last live tile of a unit; false when the unit has none.
   auto live_range = [&](int b, int mb, int t0, int t1, int& first, int& last) -> bool {
@@ -470,22 +510,49 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // else in L2. A resident row block of A is read exactly once (first out); a streamed one
   // is re-read for every column tile of the unit and keeps the default priority.
   const uint64_t a_policy = A_RES ? kL2EvictFirst : kL2EvictLast;
-  auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb, int mb, int b) {
+  // One TMA box. `bar` is the local barrier; with `to_leader` the completion bytes are
+  // counted on the same barrier of the pair's even CTA instead.
+  auto tma_issue = [&](uint8_t* dst, const CUtensorMap* map, uint64_t* bar, bool to_leader, int c0, int c1, int c2,
+                       uint64_t policy) {
+    if (PAIR && to_leader) tma_load_3d_pair(dst, map, bars_cta0 + bar_off(bar), c0, c1, c2, policy);
+    else tma_load_3d(dst, map, bar, c0, c1, c2, policy);
+  };
+  // this CTA's 128 rows of A, k-block kb
+  auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int mb, int b) {
     if (!shape.a_mn) {
-      tma_load_3d(dst, map, bar, kb * kKBlock, mb * kTileM, b, a_policy);
+      tma_issue(dst, map, bar, to_leader, kb * kKBlock, row_base(mb), b, a_policy);
     } else {
 #pragma unroll
       for (int c = 0; c < kTileM / 32; ++c)
-        tma_load_3d(dst + c * 4096, map, bar, mb * kTileM + c * 32, kb * kKBlock, b, a_policy);
+        tma_issue(dst + c * 4096, map, bar, to_leader, row_base(mb) + c * 32, kb * kKBlock, b, a_policy);
     }
   };
-  auto load_b = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb, int t, int b) {
+  // this CTA's columns of B tile t (all 128, or its 64 of a pair), k-block kb
+  auto load_b = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int t, int b) {
+    const int col = t * TILE_N + static_cast<int>(cta_rank) * kBCols;
     if (!shape.b_mn) {
-      tma_load_3d(dst, map, bar, kb * kKBlock, t * TILE_N, b, kL2EvictLast);
+      tma_issue(dst, map, bar, to_leader, kb * kKBlock, col, b, kL2EvictLast);
     } else {
 #pragma unroll
-      for (int c = 0; c < TILE_N / 32; ++c)
-        tma_load_3d(dst + c * 4096, map, bar, t * TILE_N + c * 32, kb * kKBlock, b, kL2EvictLast);
+      for (int c = 0; c < kBCols / 32; ++c)
+        tma_issue(dst + c * 4096, map, bar, to_leader, col + c * 32, kb * kKBlock, b, kL2EvictLast);
+    }
+  };
+
+  // Barriers that gate the MMAs live in the pair's even CTA: the peer arrives through the
+  // cluster window, the issuer waits with cluster scope, and commits release both CTAs.
+  auto arrive_leader = [&](uint64_t* bar) {
+    if (PAIR) mbar_arrive_cluster(bars_cta0 + bar_off(bar)); else mbar_arrive(bar);
+  };
+  auto wait_gate = [&](uint64_t* bar, uint32_t parity) -> bool {
+    return PAIR ? mbar_wait_cluster(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag);
+  };
+  auto commit_all = [&](uint64_t* bar) {
+    if (PAIR) {
+      umma_commit_pair(bars_cta0 + bar_off(bar));
+      umma_commit_pair(bars_cta1 + bar_off(bar));
+    } else {
+      umma_commit(bar);
     }
   };
 
@@ -496,7 +563,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       FBMM_PROF_DECL;
       const long long prof_start = clock64();
-      for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      for (long long u = unit_first; u < units && ok; u += unit_step) {
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range(b, mb, t0, t1, first, last)) continue;
@@ -509,20 +576,26 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               ok = mbar_wait(&bars->a_empty[kb], a_phase ^ 1u, abort_flag);
               if (!ok) break;
               mbar_arrive_expect_tx(&bars->a_full[kb], kPlaneBytes);
-              load_a(&tmap_a, a_region + kb * 2 * kPlaneBytes + off_a_hi, &bars->a_full[kb], kb, mb, b);
+              load_a(&tmap_a, a_region + kb * 2 * kPlaneBytes + off_a_hi, &bars->a_full[kb], false, kb, mb, b);
             }
             FBMM_PROF_BEGIN();
             ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag);
             FBMM_PROF_END(0);
             if (!ok) break;
             uint8_t* sb = ring + stage * plan.stage_bytes;
-            mbar_arrive_expect_tx(&bars->full[stage], (A_RES ? 1u : 2u) * (PRESPLIT ? 2u : 1u) * kPlaneBytes);
+            // bytes this CTA brings into the stage
+            constexpr uint32_t kMyBytes = ((A_RES ? 0u : kPlaneBytes) + kBPlane) * (PRESPLIT ? 2u : 1u);
+            // With pre-split planes nothing stands between the copies and the MMAs, so a
+            // pair counts both CTAs' bytes on the even CTA's barrier, which that CTA arms.
+            constexpr bool kToLeader = PAIR && PRESPLIT;
+            if (!kToLeader) mbar_arrive_expect_tx(&bars->full[stage], kMyBytes);
+            else if (cta_rank == 0) mbar_arrive_expect_tx(&bars->full[stage], 2u * kMyBytes);
             if (!A_RES) {
-              load_a(&tmap_a, sb + off_a_hi, &bars->full[stage], kb, mb, b);
-              if (PRESPLIT) load_a(&tmap_a_lo, sb + off_a_lo, &bars->full[stage], kb, mb, b);
+              load_a(&tmap_a, sb + off_a_hi, &bars->full[stage], kToLeader, kb, mb, b);
+              if (PRESPLIT) load_a(&tmap_a_lo, sb + off_a_lo, &bars->full[stage], kToLeader, kb, mb, b);
             }
-            load_b(&tmap_b, sb + off_b_hi, &bars->full[stage], kb, t, b);
-            if (PRESPLIT) load_b(&tmap_b_lo, sb + off_b_lo, &bars->full[stage], kb, t, b);
+            load_b(&tmap_b, sb + off_b_hi, &bars->full[stage], kToLeader, kb, t, b);
+            if (PRESPLIT) load_b(&tmap_b_lo, sb + off_b_lo, &bars->full[stage], kToLeader, kb, t, b);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
         }
@@ -541,32 +614,44 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {
       // A ring stage holds the B hi plane directly followed by the B lo plane, so one MMA
       // of width 2 * TILE_N over both computes hi*hi into the big accumulator and hi*lo
       // into the small one next to it while reading A_hi once.
       static_assert(2 * TILE_N <= 256, "the merged hi|lo MMA needs 2 * TILE_N <= 256");
       const uint32_t idesc = make_idesc_tf32(kTileM, TILE_N, shape.a_mn != 0, shape.b_mn != 0);
       const uint32_t idesc_wide = make_idesc_tf32(kTileM, 2 * TILE_N, shape.a_mn != 0, shape.b_mn != 0);
+      // pair: M = 256 over both CTAs; each CTA's half of B is its own stage, so the three
+      // products are three MMAs of width TILE_N (64 cycles each at this width)
+      const uint32_t idesc_pair = make_idesc_tf32(2 * kTileM, TILE_N, shape.a_mn != 0, shape.b_mn != 0);
       const uint32_t a_lbo = shape.a_mn ? 4096u : 16u, a_sbo = shape.a_mn ? 512u : 1024u;
       const uint32_t b_lbo = shape.b_mn ? 4096u : 16u, b_sbo = shape.b_mn ? 512u : 1024u;
       const uint32_t a_kstep = shape.a_mn ? 1024u : 32u, b_kstep = shape.b_mn ? 1024u : 32u;
-      const uint64_t a_type = shape.a_mn ? (1ull << 61) : (2ull << 61);
-      const uint64_t b_type = shape.b_mn ? (1ull << 61) : (2ull << 61);
-      auto desc = [](uint32_t addr, uint32_t lbo, uint32_t sbo, uint64_t type) -> uint64_t {
-        return (make_smem_desc_sw128(addr, lbo, sbo) & ~(7ull << 61)) | type;
+      // One thread has to issue an MMA every 64 cycles, so the shared-memory descriptors are
+      // kept as two 32-bit halves: the upper half (stride offset, version, layout type) is a
+      // constant per operand, the lower half is (address >> 4) | (lbo >> 4) << 16 and moves
+      // by a constant per k-step. Building each descriptor from scratch made the issuing
+      // thread, not the tensor core, the limit.
+      const uint32_t a_desc_hi = (a_sbo >> 4) | (1u << 14) | ((shape.a_mn ? 1u : 2u) << 29);
+      const uint32_t b_desc_hi = (b_sbo >> 4) | (1u << 14) | ((shape.b_mn ? 1u : 2u) << 29);
+      const uint32_t a_lbo_bits = ((a_lbo >> 4) & 0x3fffu) << 16, b_lbo_bits = ((b_lbo >> 4) & 0x3fffu) << 16;
+      const uint32_t a_step = a_kstep >> 4, b_step = b_kstep >> 4;
+      auto pack = [](uint32_t lo, uint32_t hi) -> uint64_t {
+        uint64_t d;
+        asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+        return d;
       };
       uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, a_phase = 0;
       bool ok = true;
       FBMM_PROF_DECL;
-      for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      for (long long u = unit_first; u < units && ok; u += unit_step) {
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range(b, mb, t0, t1, first, last)) continue;
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
           FBMM_PROF_BEGIN();
-          ok = mbar_wait(&bars->acc_empty[acc_stage], acc_phase ^ 1u, abort_flag);
+          ok = wait_gate(&bars->acc_empty[acc_stage], acc_phase ^ 1u);
           FBMM_PROF_END(0);
           if (!ok) break;
           tcgen05_fence_after_sync();
@@ -574,33 +659,56 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t acc_small = acc_big + TILE_N;
           for (int kb = 0; kb < kblocks; ++kb) {
             if (A_RES && t == first) {
-              ok = mbar_wait(&bars->a_split[kb], a_phase, abort_flag);
+              ok = wait_gate(&bars->a_split[kb], a_phase);
               if (!ok) break;
             }
             FBMM_PROF_BEGIN();
-            ok = mbar_wait(PRESPLIT ? &bars->full[stage] : &bars->split[stage], phase, abort_flag);
+            ok = wait_gate(PRESPLIT ? &bars->full[stage] : &bars->split[stage], phase);
             FBMM_PROF_END(1);
             if (!ok) break;
-            tcgen05_fence_after_sync();
+            // (no tcgen05 fence here: the operands reach shared memory through the async
+            // proxy, or through writers that ran fence.proxy.async before arriving)
             FBMM_PROF_BEGIN();
             const uint32_t sb = smem_u32(ring + stage * plan.stage_bytes);
             const uint32_t sa = A_RES ? smem_u32(a_region + kb * 2 * kPlaneBytes) : sb;
+            // Issue order: all four k-steps of one operand-plane combination before the
+            // next combination. Consecutive MMAs then walk the same 128-byte shared-memory
+            // rows, and the tensor core runs at its full rate (measured on pairs: 64 cycles
+            // per MMA, against 106 when the combinations alternate inside a k-step).
+            const uint32_t first_kb = kb == 0 ? 0u : 1u;
+            const uint32_t a_hi0 = ((sa + off_a_hi) >> 4) | a_lbo_bits, a_lo0 = ((sa + off_a_lo) >> 4) | a_lbo_bits;
+            const uint32_t b_hi0 = ((sb + off_b_hi) >> 4) | b_lbo_bits, b_lo0 = ((sb + off_b_lo) >> 4) | b_lbo_bits;
+            if (PAIR) {
 #pragma unroll
-            for (int ks = 0; ks < kKBlock / 8; ++ks) {
-              const uint64_t a_hi = desc(sa + off_a_hi + ks * a_kstep, a_lbo, a_sbo, a_type);
-              const uint64_t a_lo = desc(sa + off_a_lo + ks * a_kstep, a_lbo, a_sbo, a_type);
-              const uint64_t b_hi = desc(sb + off_b_hi + ks * b_kstep, b_lbo, b_sbo, b_type);
-              const uint32_t acc = (kb | ks) != 0 ? 1u : 0u;
-              umma_tf32(acc_big, a_hi, b_hi, idesc_wide, acc);  // [big | small] (+)= A_hi * [B_hi | B_lo]
-              umma_tf32(acc_small, a_lo, b_hi, idesc, 1u);      // small += A_lo * B_hi
+              for (int ks = 0; ks < kKBlock / 8; ++ks)  // small (+)= A_lo * B_hi
+                umma_tf32_pair(acc_small, pack(a_lo0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi),
+                               idesc_pair, ks == 0 ? first_kb : 1u);
+#pragma unroll
+              for (int ks = 0; ks < kKBlock / 8; ++ks)  // small += A_hi * B_lo
+                umma_tf32_pair(acc_small, pack(a_hi0 + ks * a_step, a_desc_hi), pack(b_lo0 + ks * b_step, b_desc_hi),
+                               idesc_pair, 1u);
+#pragma unroll
+              for (int ks = 0; ks < kKBlock / 8; ++ks)  // big (+)= A_hi * B_hi
+                umma_tf32_pair(acc_big, pack(a_hi0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi),
+                               idesc_pair, ks == 0 ? first_kb : 1u);
+            } else {
+#pragma unroll
+              for (int ks = 0; ks < kKBlock / 8; ++ks)  // [big | small] (+)= A_hi * [B_hi | B_lo]
+                umma_tf32(acc_big, pack(a_hi0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi),
+                          idesc_wide, ks == 0 ? first_kb : 1u);
+#pragma unroll
+              for (int ks = 0; ks < kKBlock / 8; ++ks)  // small += A_lo * B_hi
+                umma_tf32(acc_small, pack(a_lo0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi), idesc,
+                          1u);
+              (void)b_lo0;
             }
-            umma_commit(&bars->empty[stage]);
-            if (A_RES && t == last) umma_commit(&bars->a_empty[kb]);
+            commit_all(&bars->empty[stage]);
+            if (A_RES && t == last) commit_all(&bars->a_empty[kb]);
             FBMM_PROF_END(2);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
           if (!ok) break;
-          umma_commit(&bars->acc_full[acc_stage]);
+          commit_all(&bars->acc_full[acc_stage]);
           if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
         }
         a_phase ^= 1u;
@@ -616,7 +724,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t stage = 0, phase = 0, a_phase = 0;
     bool ok = true;
     FBMM_PROF_DECL;
-    for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+    for (long long u = unit_first; u < units && ok; u += unit_step) {
       int b, mb, t0, t1, first, last;
       decode(u, b, mb, t0, t1);
       if (!live_range(b, mb, t0, t1, first, last)) continue;
@@ -630,7 +738,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint8_t* ab = a_region + kb * 2 * kPlaneBytes;
             split_plane(ab + off_a_hi, ab + off_a_lo, kPlaneBytes, st);
             fence_proxy_async_smem();
-            mbar_arrive(&bars->a_split[kb]);
+            arrive_leader(&bars->a_split[kb]);
           }
           if (PRESPLIT) continue;
           FBMM_PROF_BEGIN();
@@ -640,11 +748,11 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           FBMM_PROF_BEGIN();
           uint8_t* sb = ring + stage * plan.stage_bytes;
           if (!A_RES) split_plane(sb + off_a_hi, sb + off_a_lo, kPlaneBytes, st);
-          split_plane(sb + off_b_hi, sb + off_b_lo, kPlaneBytes, st);
+          split_plane(sb + off_b_hi, sb + off_b_lo, kBPlane, st);
           FBMM_PROF_END(1);
           FBMM_PROF_BEGIN();
           fence_proxy_async_smem();
-          mbar_arrive(&bars->split[stage]);
+          arrive_leader(&bars->split[stage]);
           FBMM_PROF_END(2);
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
@@ -671,10 +779,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // top-k staging: 8-byte (value, column) entries, slot-major [slot][row]
     int2* stg = reinterpret_cast<int2*>(epi_smem);
 
-    for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+    for (long long u = unit_first; u < units && ok; u += unit_step) {
       int b, mb, t0, t1;
       decode(u, b, mb, t0, t1);
-      const int row = mb * kTileM + row_in_tile;
+      const int row = row_base(mb) + row_in_tile;
       const bool row_ok = row < shape.M;
 
       // squared-l2 mode: this row's squared norm
@@ -690,21 +798,23 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool has_list = false;
       // list of this warp's first row (rows of a warp are consecutive)
       const long long warp_row0 = (shape.tiles_per_chunk > 0 ? (t0 / shape.tiles_per_chunk) : 0) * epi.topk_chunk_rows +
-                                  static_cast<long long>(b) * shape.M + mb * kTileM + static_cast<int>(quarter) * 32;
+                                  static_cast<long long>(b) * shape.M + row_base(mb) + static_cast<int>(quarter) * 32;
       float* lv0 = (EPI == kEpiTopk) ? epi.topk_values + warp_row0 * epi.k : nullptr;
       long long* li0 = (EPI == kEpiTopk) ? epi.topk_indices + warp_row0 * epi.k : nullptr;
       const int2* stg_w = stg + quarter * 32;
 
       for (int t = t0; t < t1 && ok; ++t) {
         const int col_tile = t * TILE_N;
-        if (!tile_live(b, mb, t)) {
-          // masked-out tile: the product is defined as zero (mbmm.py:74 pre-zeroes C).
+        const bool any_live = tile_live(b, mb, t);      // loads and MMAs happen for this tile
+        const bool own_live = tile_live_own(b, mb, t);  // this CTA's 128x128 block keeps something
+        if (!own_live) {
+          // masked-out block: the product is defined as zero (mbmm.py:74 pre-zeroes C).
           if (EPI == kEpiMask) {
             const int c_end = min(shape.N, col_tile + TILE_N);
             if (c_lines_ok && col_tile + TILE_N <= shape.N) {
               // four lanes per row: every store instruction writes eight whole lines
               const int q = static_cast<int>(lane & 3u);
-              const int row_g = mb * kTileM + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
+              const int row_g = row_base(mb) + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
               float* cbase = epi.C + b * epi.stride_c + static_cast<long long>(row_g) * epi.ldc + col_tile + 8 * q;
 #pragma unroll
               for (int i = 0; i < 4; ++i)
@@ -718,6 +828,16 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int c = col_tile; c < c_end; ++c) crow[c] = 0.f;
             }
           }
+        }
+        if (!any_live) continue;
+        if (!own_live) {
+          // the pair computed this tile for the peer's block: just hand the stage back
+          ok = mbar_wait(&bars->acc_full[acc_stage], acc_phase, abort_flag);
+          if (!ok) break;
+          tcgen05_fence_after_sync();
+          tcgen05_fence_before_sync();
+          arrive_leader(&bars->acc_empty[acc_stage]);
+          if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
           continue;
         }
         FBMM_PROF_BEGIN();
@@ -740,7 +860,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (c == TILE_N / 32 - 1) {
             // both accumulators of this stage are now in registers: hand the stage back
             tcgen05_fence_before_sync();
-            mbar_arrive(&bars->acc_empty[acc_stage]);
+            arrive_leader(&bars->acc_empty[acc_stage]);
           }
           float v[32];
 #pragma unroll
@@ -776,7 +896,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               // the quad's four rows, so masks are read and C is written 4 lanes per row.
               transpose_rows_in_lane_quads(v);
               const int q = static_cast<int>(lane & 3u);
-              const int row_g = mb * kTileM + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
+              const int row_g = row_base(mb) + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
               float* cbase = epi.C + b * epi.stride_c + static_cast<long long>(row_g) * epi.ldc + col0 + 8 * q;
               if (EPI == kEpiMask) {
                 // kernels/mbmm.cu:360-363 (8x8 tile skip) and :111-133 (element multiply);
@@ -933,11 +1053,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   // ------------------------------------------------------------------ teardown
   tcgen05_fence_before_sync();
-  __syncthreads();
+  // a pair leaves together: the issuer reads the peer's shared memory and signals its barriers
+  if (PAIR) cluster_sync_all(); else __syncthreads();
   if (threadIdx.x == 0 && *abort_flag != 0) atomicOr(&g_fbmm_status[0], 1u);
   if (warp == 1) {
     tcgen05_fence_after_sync();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
