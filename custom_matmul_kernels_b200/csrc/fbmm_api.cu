@@ -667,60 +667,50 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
 // ---------------------------------------------------------------------------------------
 namespace fbmm {
 
-// One warp per row. The running list lives in the output row; each group's list is fed
-// to the rank merge 32 candidates at a time, and because the lists are sorted a group is
-// left as soon as its next candidates cannot beat the current k-th value.
+// One warp per row. The running list stays in registers (striped over the lanes); every
+// group's list is already sorted, so it is merged whole by topk_merge_lists, and skipped
+// when its best entry cannot beat the current k-th value. Entries carry their source slot
+// (group * k + position) instead of the 64-bit index, which is fetched at the end; equal
+// values therefore keep the order (group, position), which is ascending index order when
+// the groups cover ascending index ranges.
 template <int E>
 __global__ void __launch_bounds__(128) fbmm_topk_merge_kernel(const float* __restrict__ cv, const long long* __restrict__ ci,
                                                               int groups, long long rows, int k, float* ov, long long* oi) {
   const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;  // whole warps leave together
   const int lane = static_cast<int>(lane_id());
+  float L[E];
+  int LI[E];
+#pragma unroll
+  for (int j = 0; j < E; ++j) { L[j] = -INFINITY; LI[j] = kTopkEmpty; }
+  float thr = -INFINITY;
+  for (int g = 0; g < groups; ++g) {
+    const float* gv = cv + (static_cast<long long>(g) * rows + row) * k;
+    const long long* gi = ci + (static_cast<long long>(g) * rows + row) * k;
+    float G[E];
+    int GI[E];
+#pragma unroll
+    for (int j = 0; j < E; ++j) {
+      const int i = j * 32 + lane;
+      G[j] = -INFINITY;
+      GI[j] = kTopkEmpty;
+      if (i < k && gi[i] >= 0) { G[j] = gv[i]; GI[j] = g * k + i; }
+    }
+    const float g0 = __shfl_sync(0xffffffffu, G[0], 0);
+    if (g > 0 && !(g0 > thr)) continue;  // sorted: nothing in this group can enter
+    topk_merge_lists<E>(L, LI, G, GI);
+    thr = topk_list_entry<E>(L, k - 1);
+  }
   float* lv = ov + row * k;
   long long* li = oi + row * k;
 #pragma unroll
   for (int j = 0; j < E; ++j) {
     const int i = j * 32 + lane;
-    if (i < k) { lv[i] = -INFINITY; li[i] = -1ll; }
-  }
-  __syncwarp();
-  float thr = -INFINITY;
-  for (int g = 0; g < groups; ++g) {
-    const float* gv = cv + (static_cast<long long>(g) * rows + row) * k;
-    const long long* gi = ci + (static_cast<long long>(g) * rows + row) * k;
-    for (int c0 = 0; c0 < k; c0 += 32) {
-      const int i = c0 + lane;
-      float v = -INFINITY;
+    if (i < k) {
+      lv[i] = L[j];
       long long id = -1;
-      if (i < k) { v = gv[i]; id = gi[i]; }
-      const bool pass = id >= 0 && v > thr;
-      const uint32_t pm = __ballot_sync(0xffffffffu, pass);
-      if (pm == 0) break;  // sorted: nothing further in this group can enter
-      // compact the passing candidates to lanes [0, cnt)
-      const int cnt = __popc(pm);
-      const int dst = __popc(pm & ((1u << lane) - 1u));
-      float cvv = -INFINITY;
-      int cii = kTopkEmpty;
-      for (int s = 0; s < 32; ++s) {
-        const float sv = __shfl_sync(0xffffffffu, v, s);
-        const int si = __shfl_sync(0xffffffffu, static_cast<int>(id), s);
-        const int sd = __shfl_sync(0xffffffffu, dst, s);
-        if (((pm >> s) & 1u) && sd == lane) { cvv = sv; cii = si; }
-      }
-      float L[E];
-      int LI[E];
-#pragma unroll
-      for (int j = 0; j < E; ++j) {
-        const int q = j * 32 + lane;
-        L[j] = -INFINITY;
-        LI[j] = kTopkEmpty;
-        if (q < k) {
-          L[j] = lv[q];
-          const long long t = li[q];
-          LI[j] = t < 0 ? kTopkEmpty : static_cast<int>(t);
-        }
-      }
-      thr = topk_rank_merge<E>(L, LI, cvv, cii, cnt, k, lv, li, 0);
+      if (LI[j] != kTopkEmpty) id = ci[(static_cast<long long>(LI[j] / k) * rows + row) * k + (LI[j] % k)];
+      li[i] = id;
     }
   }
 }
@@ -733,6 +723,7 @@ extern "C" int fbmm_topk_merge_f32(void* stream, const float* cand_values, const
     return fail(FBMM_ERR_INVALID, "a pointer is null");
   if (groups <= 0 || rows <= 0) return fail(FBMM_ERR_INVALID, "groups and rows must be positive");
   if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
+  if (groups > (1 << 23)) return fail(FBMM_ERR_INVALID, "at most %d groups", 1 << 23);  // slot ids stay below 2^31
   const long long blocks = (rows + 3) / 4;
   if (blocks > 0x7fffffffll) return fail(FBMM_ERR_INVALID, "too many rows");
   cudaStream_t s = static_cast<cudaStream_t>(stream);

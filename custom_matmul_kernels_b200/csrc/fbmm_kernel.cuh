@@ -204,71 +204,82 @@ __device__ __forceinline__ void topk_stage_if(uint32_t pred, uint32_t addr, floa
       : "memory");
 }
 
-// Rank merge of up to 32 unsorted candidates (one per lane, lanes [0, cnt)) into a
-// descending list of k entries spread over the warp (entry i in lane i % 32, slot i / 32).
-// Every list entry moves down by the number of candidates that precede it, every
-// candidate lands at (list entries that precede it) + (candidates that precede it);
-// positions >= k fall off the end. The new list is scattered to lv / li (list storage,
-// indices written with `index_offset` added) and the new k-th value is returned to all
-// lanes. Order: larger value first, ties by lower index; empty slots (-inf, kTopkEmpty)
-// sort last. Takes the place of the reference's sort-then-merge networks
-// (bitonic_sort_128 + bitonic_sort_256, kernels/topkbmm.cu:98-183): the list is already
-// sorted and only a few candidates arrive at a time, so ranking them costs O(cnt) per
-// lane instead of a full sorting network.
+// Sorts a bitonic sequence of 32 * E striped pairs (entry i in lane i % 32, slot i / 32)
+// into descending order: the last log2(32 E) stages of the sorting network.
 template <int E>
-__device__ __forceinline__ float topk_rank_merge(const float (&L)[E], const int (&LI)[E], float cv, int ci, int cnt,
-                                                 int k, float* lv, long long* li, long long index_offset) {
-  const int lane = static_cast<int>(lane_id());
-  int add[E];
+__device__ __forceinline__ void warp_bitonic_merge_desc(float (&v)[E], int (&ix)[E]) {
+  const uint32_t lane = lane_id();
 #pragma unroll
-  for (int j = 0; j < E; ++j) add[j] = 0;
-  int my_pos = 0;
-  for (int c = 0; c < cnt; ++c) {
-    const float bv = __shfl_sync(0xffffffffu, cv, c);
-    const int bi = __shfl_sync(0xffffffffu, ci, c);
-    int list_before = 0;
+  for (int stride = 16 * E; stride > 0; stride >>= 1) {
+    if (stride >= 32) {
+      const int js = stride >> 5;
 #pragma unroll
-    for (int j = 0; j < E; ++j) {
-      const bool cand_first = topk_before(bv, bi, L[j], LI[j]);
-      add[j] += cand_first ? 1 : 0;
-      const bool slot = (j * 32 + lane) < k;
-      list_before += __popc(__ballot_sync(0xffffffffu, slot && !cand_first));
+      for (int j = 0; j < E; ++j) {
+        if ((j & js) == 0 && !topk_before(v[j], ix[j], v[j | js], ix[j | js])) {
+          const float tv = v[j]; v[j] = v[j | js]; v[j | js] = tv;
+          const int tx = ix[j]; ix[j] = ix[j | js]; ix[j | js] = tx;
+        }
+      }
+    } else {
+      const bool lower = ((lane & stride) == 0);
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v[j], stride);
+        const int oi = __shfl_xor_sync(0xffffffffu, ix[j], stride);
+        const bool mine_first = topk_before(v[j], ix[j], ov, oi);
+        if (mine_first != lower) { v[j] = ov; ix[j] = oi; }
+      }
     }
-    if (lane == c) my_pos += list_before;
-    else if (lane < cnt && topk_before(bv, bi, cv, ci)) my_pos += 1;
   }
-  __syncwarp();
-  float kth = -INFINITY;
-  bool have = false;
+}
+
+// Merges 32 candidates, sorted descending across the lanes (best in lane 0), into a
+// descending striped list of 32 * E entries and keeps the best 32 * E. Entry i of the
+// result is the better of list[i] and candidate[32 E - 1 - i] (only the last slot has a
+// candidate to meet), which leaves the survivors as a bitonic sequence; log2(32 E) merge
+// stages sort it. Order: larger value first, ties by lower index; empty entries
+// (-inf, kTopkEmpty) sort last. Takes the place of the reference's sort-then-merge
+// networks (bitonic_sort_128 + bitonic_sort_256, kernels/topkbmm.cu:98-183).
+template <int E>
+__device__ __forceinline__ void topk_merge_sorted32(float (&L)[E], int (&LI)[E], float cv, int ci) {
+  const int partner = 31 - static_cast<int>(lane_id());
+  const float bv = __shfl_sync(0xffffffffu, cv, partner);
+  const int bi = __shfl_sync(0xffffffffu, ci, partner);
+  if (topk_before(bv, bi, L[E - 1], LI[E - 1])) { L[E - 1] = bv; LI[E - 1] = bi; }
+  warp_bitonic_merge_desc<E>(L, LI);
+}
+
+// Same for two descending striped lists of 32 * E entries each; the result replaces L.
+template <int E>
+__device__ __forceinline__ void topk_merge_lists(float (&L)[E], int (&LI)[E], const float (&G)[E], const int (&GI)[E]) {
+  const int partner = 31 - static_cast<int>(lane_id());
 #pragma unroll
   for (int j = 0; j < E; ++j) {
-    const int i = j * 32 + lane;
-    const int p = i + add[j];
-    if (i < k && p < k) {
-      if (add[j] != 0) {  // unmoved entries are already in place
-        lv[p] = L[j];
-        li[p] = (LI[j] == kTopkEmpty) ? -1ll : static_cast<long long>(LI[j]) + index_offset;
-      }
-      if (p == k - 1) { kth = L[j]; have = true; }
-    }
+    const float bv = __shfl_sync(0xffffffffu, G[E - 1 - j], partner);
+    const int bi = __shfl_sync(0xffffffffu, GI[E - 1 - j], partner);
+    if (topk_before(bv, bi, L[j], LI[j])) { L[j] = bv; LI[j] = bi; }
   }
-  if (lane < cnt && my_pos < k) {
-    lv[my_pos] = cv;
-    li[my_pos] = static_cast<long long>(ci) + index_offset;
-    if (my_pos == k - 1) { kth = cv; have = true; }
-  }
-  const uint32_t who = __ballot_sync(0xffffffffu, have);
-  kth = __shfl_sync(0xffffffffu, kth, who ? (__ffs(who) - 1) : 0);
-  __syncwarp();
-  return kth;
+  warp_bitonic_merge_desc<E>(L, LI);
+}
+
+// Entry `pos` of a striped list, delivered to every lane.
+template <int E>
+__device__ __forceinline__ float topk_list_entry(const float (&L)[E], int pos) {
+  float x = L[0];
+#pragma unroll
+  for (int j = 1; j < E; ++j)
+    if ((pos >> 5) == j) x = L[j];
+  return __shfl_sync(0xffffffffu, x, pos & 31);
 }
 
 // Merges, for every row of this warp flagged in `need`, the row's staged candidates
 // (at most 32) into its running list (k entries, descending, kept in the output
 // buffers) and returns the caller lane's new threshold (the k-th best) when its own row
-// was flagged, else `thr` unchanged. Rows are handled one after the other by the whole
-// warp. `has_list` flags rows whose list has been written before; the others start from
-// an empty list (-inf / -1 padding). Called by all 32 lanes.
+// was flagged, else `thr` unchanged. The whole warp works on a row: the candidates are
+// sorted across the lanes, then merged into the list by topk_merge_sorted32. Two rows are
+// in flight at a time, because one row's chain of dependent shuffles leaves the warp idle
+// most cycles. `has_list` flags rows whose list has been written before; the others start
+// from an empty list. Called by all 32 lanes.
 //   lv0 / li0: list of the warp's first row; stg: staging entries (value bits, column),
 //   slot-major [slot][128 rows], already offset to the warp's first row. A row has one owner, so no
 //   lock is needed (the reference takes a per-row spin mutex, kernels/topkbmm.cu:13-47).
@@ -276,46 +287,72 @@ template <int E>
 __device__ __noinline__ float topk_merge_rows(uint32_t need, uint32_t has_list, int n_staged, float thr,
                                               float* lv0, long long* li0, int k, long long index_offset,
                                               const int2* stg) {
+  constexpr int R = 2;
   const int lane = static_cast<int>(lane_id());
   uint32_t m = need;
   while (m) {
-    const int src = __ffs(m) - 1;
-    m &= m - 1;
-    const int cnt = __shfl_sync(0xffffffffu, n_staged, src);
-    const bool listed = (has_list >> src) & 1u;
-    float* lv = lv0 + static_cast<long long>(src) * k;
-    long long* li = li0 + static_cast<long long>(src) * k;
-    float L[E];
-    int LI[E];
+    int src[R];
+    bool live[R];
 #pragma unroll
-    for (int j = 0; j < E; ++j) {
-      const int i = j * 32 + lane;
-      L[j] = -INFINITY;
-      LI[j] = kTopkEmpty;
-      if (i < k && listed) {
-        L[j] = lv[i];
-        const long long gi = li[i];
-        LI[j] = gi < 0 ? kTopkEmpty : static_cast<int>(gi - index_offset);
-      }
+    for (int r = 0; r < R; ++r) {
+      live[r] = m != 0;
+      src[r] = live[r] ? (__ffs(m) - 1) : src[0];
+      m &= m - 1;
     }
-    float cv = -INFINITY;
-    int ci = kTopkEmpty;
-    if (lane < cnt) {
-      const int2 e = stg[lane * kTileM + src];
-      cv = __int_as_float(e.x);
-      ci = e.y;
-    }
-    if (!listed) {
-      // first write of this row: lay down the padding the rank merge will not touch
+    float L[R][E], cv[R];
+    int LI[R][E], ci[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const bool listed = (has_list >> src[r]) & 1u;
+      const float* lv = lv0 + static_cast<long long>(src[r]) * k;
+      const long long* li = li0 + static_cast<long long>(src[r]) * k;
 #pragma unroll
       for (int j = 0; j < E; ++j) {
         const int i = j * 32 + lane;
-        if (i < k) { lv[i] = -INFINITY; li[i] = -1ll; }
+        L[r][j] = -INFINITY;
+        LI[r][j] = kTopkEmpty;
+        if (i < k && listed) {
+          L[r][j] = lv[i];
+          const long long gi = li[i];
+          LI[r][j] = gi < 0 ? kTopkEmpty : static_cast<int>(gi - index_offset);
+        }
       }
-      __syncwarp();
+      const int cnt = __shfl_sync(0xffffffffu, n_staged, src[r]);
+      cv[r] = -INFINITY;
+      ci[r] = kTopkEmpty;
+      if (lane < cnt) {
+        const int2 e = stg[lane * kTileM + src[r]];
+        cv[r] = __int_as_float(e.x);
+        ci[r] = e.y;
+      }
     }
-    const float kth = topk_rank_merge<E>(L, LI, cv, ci, cnt, k, lv, li, index_offset);
-    if (lane == src) thr = kth;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      float sv[1] = {cv[r]};
+      int si[1] = {ci[r]};
+      warp_bitonic_sort_desc<1>(sv, si);
+      cv[r] = sv[0];
+      ci[r] = si[0];
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) topk_merge_sorted32<E>(L[r], LI[r], cv[r], ci[r]);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      if (live[r]) {  // warp-uniform
+        float* lv = lv0 + static_cast<long long>(src[r]) * k;
+        long long* li = li0 + static_cast<long long>(src[r]) * k;
+#pragma unroll
+        for (int j = 0; j < E; ++j) {
+          const int i = j * 32 + lane;
+          if (i < k) {
+            lv[i] = L[r][j];
+            li[i] = (LI[r][j] == kTopkEmpty) ? -1ll : static_cast<long long>(LI[r][j]) + index_offset;
+          }
+        }
+        const float kth = topk_list_entry<E>(L[r], k - 1);
+        if (lane == src[r]) thr = kth;
+      }
+    }
   }
   return thr;
 }
