@@ -575,6 +575,13 @@ static void topk_plan(int l, int rows_per_batch, int cols, int sms, int* n_chunk
   choose_chunks(l, m_blocks, n_tiles, sms, kTopkOverheadTiles, kMaxChunks, n_chunks, tiles_per_chunk);
 }
 
+// Running lists of the units in flight: one area per CTA (at most one CTA per SM), 32 E
+// entries x 128 rows of fp32 values and as many int32 columns.
+static size_t topk_scratch_bytes(int sms, int topk) {
+  const size_t list_slots = topk <= 64 ? 64 : 128;  // 32 E, as chosen at launch
+  return static_cast<size_t>(sms) * list_slots * kTileM * 8;
+}
+
 size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim, int distance) {
   (void)k;
   if (l <= 0 || m <= 0 || n <= 0 || topk <= 0) return 0;
@@ -588,7 +595,7 @@ size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int d
   }
   if (distance == FBMM_DIST_L2)
     need = align_up(need, 256) + align_up(static_cast<size_t>(l) * m * 4, 256) + align_up(static_cast<size_t>(l) * n * 4, 256);
-  return need;
+  return align_up(need, 256) + topk_scratch_bytes(sm_count_or_default(), topk);
 }
 
 int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long* cand_indices, int groups,
@@ -648,9 +655,17 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
     if ((rc = launch_norms(stream, p, static_cast<char*>(workspace) + own, &e)) != FBMM_OK) return rc;
     own = need;
   }
+  {
+    const size_t need = own + topk_scratch_bytes(st->sms, topk);
+    if (workspace == nullptr || workspace_bytes < need)
+      return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
+      return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
+    e.topk_scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + own);
+    own = need;
+  }
   void* lo_scratch = nullptr;
-  if (workspace != nullptr && (reinterpret_cast<uintptr_t>(workspace) & 255u) == 0 && presplit_worthwhile(p) &&
-      workspace_bytes >= own + presplit_bytes(p))
+  if (presplit_worthwhile(p) && workspace_bytes >= own + presplit_bytes(p))
     lo_scratch = static_cast<char*>(workspace) + own;
   if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch);  // list slots per lane
   else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e, lo_scratch);

@@ -51,6 +51,13 @@ __device__ long long g_fbmm_prof[24];
 #define FBMM_PROF_END(i) prof_acc_[i] += clock64() - prof_t0_
 #define FBMM_PROF_MARK(i, c, n) long long prof_m0_ = clock64(); prof_acc_[c] += (n)
 #define FBMM_PROF_MARK_END(i) prof_acc_[i] += clock64() - prof_m0_
+#define FBMM_PROF_PHASE_DECL long long prof_p0_ = clock64()
+#define FBMM_PROF_PHASE(i)                                                              \
+  {                                                                                     \
+    const long long now_ = clock64();                                                   \
+    if (blockIdx.x == 0 && threadIdx.x == 192) g_fbmm_prof[20 + (i)] += now_ - prof_p0_; \
+    prof_p0_ = now_;                                                                    \
+  }
 #define FBMM_PROF_FLUSH(base)                                                           \
   if (blockIdx.x == 0) {                                                                \
     for (int q_ = 0; q_ < 4; ++q_) g_fbmm_prof[(base) + q_] = prof_acc_[q_];            \
@@ -65,6 +72,8 @@ __device__ long long g_fbmm_prof[24];
 #define FBMM_PROF_MARK(i, c, n)
 #define FBMM_PROF_MARK_END(i)
 #define FBMM_PROF_FLUSH(base)
+#define FBMM_PROF_PHASE_DECL
+#define FBMM_PROF_PHASE(i)
 #endif
 
 struct GemmShape {
@@ -98,6 +107,8 @@ struct EpiArgs {
   int k;
   long long index_offset;     // added to every column index written (column shards)
   long long topk_chunk_rows;  // rows between the lists of consecutive column chunks (0: one chunk)
+  float* topk_scratch;        // running lists of the unit a CTA works on: per CTA 32 E entries x 128 rows of
+                              // values, then as many int32 columns, entry-major (see topk_merge_own_rows)
   // squared-l2 distance (min / top-k): squared norms of the row operand [L][M] and of the
   // column operand [L][N]; null for the inner product
   const float* row_norms;
@@ -116,51 +127,14 @@ __device__ __forceinline__ float split_lo(float x) {
 }
 
 // --------------------------------------------------------------------------------------
-// top-k helpers: warp-wide bitonic sort of P = 32 * E (value, index) pairs, descending by
-// value, ties broken by ascending index. Element i lives in lane (i % 32), slot (i / 32).
+// top-k helpers. Order of (value, index) pairs everywhere: larger value first, ties by
+// ascending index. In the warp-wide routines element i of a list of 32 * E lives in lane
+// (i % 32), slot (i / 32).
 // --------------------------------------------------------------------------------------
+// Bitwise operators on purpose: with the short-circuit forms the compiler emits branches,
+// and a compare-exchange then costs four times as much.
 __device__ __forceinline__ bool topk_before(float va, int ia, float vb, int ib) {
-  return (va > vb) || (va == vb && ia < ib);
-}
-
-template <int E>
-__device__ __forceinline__ void warp_bitonic_sort_desc(float (&v)[E], int (&ix)[E]) {
-  const uint32_t lane = lane_id();
-#pragma unroll
-  for (int size = 2; size <= 32 * E; size <<= 1) {
-#pragma unroll
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      if (stride >= 32) {
-        const int js = stride >> 5;
-#pragma unroll
-        for (int j = 0; j < E; ++j) {
-          if ((j & js) == 0) {
-            // descending block when bit `size` of the element index is clear; for
-            // stride >= 32 only the slot part of the index can carry that bit
-            const bool desc = (((j * 32) & size) == 0);
-            const bool first = topk_before(v[j], ix[j], v[j | js], ix[j | js]);
-            if (first != desc) {
-              const float tv = v[j]; v[j] = v[j | js]; v[j | js] = tv;
-              const int ti = ix[j]; ix[j] = ix[j | js]; ix[j | js] = ti;
-            }
-          }
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < E; ++j) {
-          const int i = j * 32 + static_cast<int>(lane);
-          const bool desc = ((i & size) == 0);
-          const bool lower = ((lane & stride) == 0);
-          const float ov = __shfl_xor_sync(0xffffffffu, v[j], stride);
-          const int oi = __shfl_xor_sync(0xffffffffu, ix[j], stride);
-          // the lower position keeps the "first" element in a descending block
-          const bool mine_first = topk_before(v[j], ix[j], ov, oi);
-          const bool keep_mine = (lower == desc) ? mine_first : !mine_first;
-          if (!keep_mine) { v[j] = ov; ix[j] = oi; }
-        }
-      }
-    }
-  }
+  return (va > vb) | ((va == vb) & (ia < ib));
 }
 
 // Within each group of four lanes, turns "lane q holds 32 consecutive columns of its own
@@ -233,23 +207,11 @@ __device__ __forceinline__ void warp_bitonic_merge_desc(float (&v)[E], int (&ix)
   }
 }
 
-// Merges 32 candidates, sorted descending across the lanes (best in lane 0), into a
-// descending striped list of 32 * E entries and keeps the best 32 * E. Entry i of the
-// result is the better of list[i] and candidate[32 E - 1 - i] (only the last slot has a
-// candidate to meet), which leaves the survivors as a bitonic sequence; log2(32 E) merge
-// stages sort it. Order: larger value first, ties by lower index; empty entries
-// (-inf, kTopkEmpty) sort last. Takes the place of the reference's sort-then-merge
-// networks (bitonic_sort_128 + bitonic_sort_256, kernels/topkbmm.cu:98-183).
-template <int E>
-__device__ __forceinline__ void topk_merge_sorted32(float (&L)[E], int (&LI)[E], float cv, int ci) {
-  const int partner = 31 - static_cast<int>(lane_id());
-  const float bv = __shfl_sync(0xffffffffu, cv, partner);
-  const int bi = __shfl_sync(0xffffffffu, ci, partner);
-  if (topk_before(bv, bi, L[E - 1], LI[E - 1])) { L[E - 1] = bv; LI[E - 1] = bi; }
-  warp_bitonic_merge_desc<E>(L, LI);
-}
-
-// Same for two descending striped lists of 32 * E entries each; the result replaces L.
+// Merges two descending striped lists of 32 * E entries each and keeps the best 32 * E in L:
+// entry i of the result is the better of L[i] and G[32 E - 1 - i], which leaves the survivors
+// as a bitonic sequence; log2(32 E) merge stages sort it. Order: larger value first, ties by
+// lower index; empty entries (-inf, kTopkEmpty) sort last. The warp-wide counterpart of the
+// reference's merge network (bitonic_sort_256, kernels/topkbmm.cu:98-183).
 template <int E>
 __device__ __forceinline__ void topk_merge_lists(float (&L)[E], int (&LI)[E], const float (&G)[E], const int (&GI)[E]) {
   const int partner = 31 - static_cast<int>(lane_id());
@@ -272,89 +234,264 @@ __device__ __forceinline__ float topk_list_entry(const float (&L)[E], int pos) {
   return __shfl_sync(0xffffffffu, x, pos & 31);
 }
 
-// Merges, for every row of this warp flagged in `need`, the row's staged candidates
-// (at most 32) into its running list (k entries, descending, kept in the output
-// buffers) and returns the caller lane's new threshold (the k-th best) when its own row
-// was flagged, else `thr` unchanged. The whole warp works on a row: the candidates are
-// sorted across the lanes, then merged into the list by topk_merge_sorted32. Two rows are
-// in flight at a time, because one row's chain of dependent shuffles leaves the warp idle
-// most cycles. `has_list` flags rows whose list has been written before; the others start
-// from an empty list. Called by all 32 lanes.
-//   lv0 / li0: list of the warp's first row; stg: staging entries (value bits, column),
-//   slot-major [slot][128 rows], already offset to the warp's first row. A row has one owner, so no
-//   lock is needed (the reference takes a per-row spin mutex, kernels/topkbmm.cu:13-47).
-template <int E>
-__device__ __noinline__ float topk_merge_rows(uint32_t need, uint32_t has_list, int n_staged, float thr,
-                                              float* lv0, long long* li0, int k, long long index_offset,
-                                              const int2* stg) {
-  constexpr int R = 2;
-  const int lane = static_cast<int>(lane_id());
-  uint32_t m = need;
-  while (m) {
-    int src[R];
-    bool live[R];
+// --------------------------------------------------------------------------------------
+// Running top-k lists inside the fused kernel: one row per lane.
+//
+// An epilogue lane owns one row of the 128-row block (it reads that row's accumulator from
+// tensor memory). Its running list lives in a per-CTA scratch area in global memory,
+// entry-major: entry e of row r at [e * 128 + r], values and int32 columns in two arrays.
+// A warp-wide access to "entry e of my row" is therefore one 128-byte line, and every lane
+// can run the merge networks on its own row in registers with uniform addresses: no
+// shuffles, 32 rows advance at once, nothing is shared between lanes. (A warp-wide merge of
+// ONE row costs a chain of ~35 dependent shuffle stages at ~30 cycles each.) The lists go
+// to the caller's [row][k] buffers once, when the unit ends. The reference keeps its lists
+// in the output buffers under a per-row spin mutex (kernels/topkbmm.cu:13-47, 249-303).
+// --------------------------------------------------------------------------------------
+
+// Compare-exchange: afterwards (va, ia) is the entry that comes first.
+__device__ __forceinline__ void topk_ce(float& va, int& ia, float& vb, int& ib) {
+  const bool sw = topk_before(vb, ib, va, ia);
+  const float tv = sw ? vb : va;
+  const int ti = sw ? ib : ia;
+  vb = sw ? va : vb;
+  ib = sw ? ia : ib;
+  va = tv;
+  ia = ti;
+}
+
+// Compare-exchange with a run-time direction: (va, ia) comes first afterwards when `desc`.
+__device__ __forceinline__ void topk_ce_dir(float& va, int& ia, float& vb, int& ib, bool desc) {
+  const bool sw = topk_before(vb, ib, va, ia) == desc;
+  const float tv = sw ? vb : va;
+  const int ti = sw ? ib : ia;
+  vb = sw ? va : vb;
+  ib = sw ? ia : ib;
+  va = tv;
+  ia = ti;
+}
+
+// The merge stages with strides 4, 2, 1 on eight register pairs, all in one direction.
+__device__ __forceinline__ void topk_merge8(float (&v)[8], int (&ix)[8], bool desc) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      live[r] = m != 0;
-      src[r] = live[r] ? (__ffs(m) - 1) : src[0];
-      m &= m - 1;
-    }
-    float L[R][E], cv[R];
-    int LI[R][E], ci[R];
+  for (int st = 4; st > 0; st >>= 1) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const bool listed = (has_list >> src[r]) & 1u;
-      const float* lv = lv0 + static_cast<long long>(src[r]) * k;
-      const long long* li = li0 + static_cast<long long>(src[r]) * k;
+    for (int e = 0; e < 8; ++e)
+      if ((e & st) == 0) topk_ce_dir(v[e], ix[e], v[e | st], ix[e | st], desc);
+  }
+}
+
+// The merge stages with strides 16 to 1 on 32 register pairs (four groups of eight),
+// descending: sorts a bitonic sequence of 32.
+__device__ __forceinline__ void topk_merge32_desc(float (&v)[4][8], int (&ix)[4][8]) {
 #pragma unroll
-      for (int j = 0; j < E; ++j) {
-        const int i = j * 32 + lane;
-        L[r][j] = -INFINITY;
-        LI[r][j] = kTopkEmpty;
-        if (i < k && listed) {
-          L[r][j] = lv[i];
-          const long long gi = li[i];
-          LI[r][j] = gi < 0 ? kTopkEmpty : static_cast<int>(gi - index_offset);
-        }
-      }
-      const int cnt = __shfl_sync(0xffffffffu, n_staged, src[r]);
-      cv[r] = -INFINITY;
-      ci[r] = kTopkEmpty;
-      if (lane < cnt) {
-        const int2 e = stg[lane * kTileM + src[r]];
-        cv[r] = __int_as_float(e.x);
-        ci[r] = e.y;
-      }
-    }
+  for (int js = 2; js > 0; js >>= 1) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) {
-      float sv[1] = {cv[r]};
-      int si[1] = {ci[r]};
-      warp_bitonic_sort_desc<1>(sv, si);
-      cv[r] = sv[0];
-      ci[r] = si[0];
-    }
+    for (int c = 0; c < 4; ++c) {
+      if ((c & js) == 0) {
 #pragma unroll
-    for (int r = 0; r < R; ++r) topk_merge_sorted32<E>(L[r], LI[r], cv[r], ci[r]);
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if (live[r]) {  // warp-uniform
-        float* lv = lv0 + static_cast<long long>(src[r]) * k;
-        long long* li = li0 + static_cast<long long>(src[r]) * k;
-#pragma unroll
-        for (int j = 0; j < E; ++j) {
-          const int i = j * 32 + lane;
-          if (i < k) {
-            lv[i] = L[r][j];
-            li[i] = (LI[r][j] == kTopkEmpty) ? -1ll : static_cast<long long>(LI[r][j]) + index_offset;
-          }
-        }
-        const float kth = topk_list_entry<E>(L[r], k - 1);
-        if (lane == src[r]) thr = kth;
+        for (int e = 0; e < 8; ++e) topk_ce(v[c][e], ix[c][e], v[c | js][e], ix[c | js][e]);
       }
     }
   }
-  return thr;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+#pragma unroll
+    for (int st = 4; st > 0; st >>= 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if ((e & st) == 0) topk_ce(v[c][e], ix[c][e], v[c][e | st], ix[c][e | st]);
+    }
+  }
+}
+
+__device__ __forceinline__ void topk_slots_load8(const int2* slots, int first, float (&v)[8], int (&ix)[8]) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const int2 t = slots[(first + e) * kTileM];
+    v[e] = __int_as_float(t.x);
+    ix[e] = t.y;
+  }
+}
+__device__ __forceinline__ void topk_slots_store8(int2* slots, int first, const float (&v)[8], const int (&ix)[8]) {
+#pragma unroll
+  for (int e = 0; e < 8; ++e) slots[(first + e) * kTileM] = make_int2(__float_as_int(v[e]), ix[e]);
+}
+
+// Bitonic sorting network over the 32 staging slots of one lane (slots kTileM entries
+// apart, so the lanes of a warp never meet in a bank), descending. Three trips through
+// shared memory, each doing in registers every stage that stays inside what it loaded:
+// groups of 8 (sizes 2, 4, 8), pairs of groups (size 16), all four groups (size 32).
+__device__ __forceinline__ void thread_sort32_desc(int2* slots) {
+#pragma unroll 1
+  for (int g = 0; g < 4; ++g) {
+    float v[8];
+    int ix[8];
+    topk_slots_load8(slots, 8 * g, v, ix);
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) topk_ce_dir(v[e], ix[e], v[e + 1], ix[e + 1], (e & 2) == 0);
+#pragma unroll
+    for (int st = 2; st > 0; st >>= 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if ((e & st) == 0) topk_ce_dir(v[e], ix[e], v[e | st], ix[e | st], (e & 4) == 0);
+    }
+    topk_merge8(v, ix, (g & 1) == 0);
+    topk_slots_store8(slots, 8 * g, v, ix);
+  }
+#pragma unroll 1
+  for (int h = 0; h < 2; ++h) {
+    float v[2][8];
+    int ix[2][8];
+    topk_slots_load8(slots, 16 * h, v[0], ix[0]);
+    topk_slots_load8(slots, 16 * h + 8, v[1], ix[1]);
+    const bool desc = h == 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) topk_ce_dir(v[0][e], ix[0][e], v[1][e], ix[1][e], desc);
+    topk_merge8(v[0], ix[0], desc);
+    topk_merge8(v[1], ix[1], desc);
+    topk_slots_store8(slots, 16 * h, v[0], ix[0]);
+    topk_slots_store8(slots, 16 * h + 8, v[1], ix[1]);
+  }
+  {
+    float v[4][8];
+    int ix[4][8];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) topk_slots_load8(slots, 8 * c, v[c], ix[c]);
+    topk_merge32_desc(v, ix);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) topk_slots_store8(slots, 8 * c, v[c], ix[c]);
+  }
+}
+
+// Every lane merges its own row's staged candidates (n_staged of them, at most 32, in the
+// lane's staging slots) into its own list and returns the row's new k-th value.
+// The list has room for 32 E entries in blocks of 32; the first ceil(k / 32) blocks are
+// kept (sorted, descending), the rest always read as empty.
+//   1. the candidates are padded to 32 and sorted in place in the staging slots;
+//   2. first pass over the list, eight entries of every block at a time: the last block
+//      meets the candidates in reverse order (keeping the better of each pair leaves the
+//      best 32 E of list and candidates as a bitonic sequence), then the merge stages
+//      whose stride is a multiple of 32 run across the blocks;
+//   3. second pass, block by block: strides 16 to 1, all in registers. Blocks past the
+//      k-th entry hold nothing that can reach the first k places any more and are dropped.
+// `listed` (warp-uniform): the lists have been written in this unit; otherwise they start
+// empty. sv / si: entry 0 of the lane's own row in the scratch arrays.
+template <int E>
+__device__ __noinline__ float topk_merge_own_rows(bool listed, int n_staged, float* sv, int* si, int k, int2* stg_own) {
+  const int live_blocks = (k + 31) >> 5;
+  FBMM_PROF_PHASE_DECL;
+  for (int sl = n_staged; sl < 32; ++sl) stg_own[sl * kTileM] = make_int2(__float_as_int(-INFINITY), kTopkEmpty);
+  __syncwarp();
+  thread_sort32_desc(stg_own);
+  FBMM_PROF_PHASE(0);
+#pragma unroll 1
+  for (int c = 0; c < 4; ++c) {
+    float v[E][8];
+    int ix[E][8];
+#pragma unroll
+    for (int b = 0; b < E; ++b) {
+      const bool use = listed && b < live_blocks;  // warp-uniform
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[b][e] = -INFINITY;
+        ix[b][e] = kTopkEmpty;
+        if (use) {
+          v[b][e] = sv[(32 * b + 8 * c + e) * kTileM];
+          ix[b][e] = si[(32 * b + 8 * c + e) * kTileM];
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      // list entry 32 E - 32 + j meets candidate 31 - j
+      const int2 cand = stg_own[(31 - (8 * c + e)) * kTileM];
+      if (topk_before(__int_as_float(cand.x), cand.y, v[E - 1][e], ix[E - 1][e])) {
+        v[E - 1][e] = __int_as_float(cand.x);
+        ix[E - 1][e] = cand.y;
+      }
+    }
+#pragma unroll
+    for (int js = E >> 1; js > 0; js >>= 1) {
+#pragma unroll
+      for (int b = 0; b < E; ++b) {
+        if ((b & js) == 0) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) topk_ce(v[b][e], ix[b][e], v[b | js][e], ix[b | js][e]);
+        }
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < E; ++b) {
+      if (b < live_blocks) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          sv[(32 * b + 8 * c + e) * kTileM] = v[b][e];
+          si[(32 * b + 8 * c + e) * kTileM] = ix[b][e];
+        }
+      }
+    }
+  }
+  FBMM_PROF_PHASE(1);
+  float kth = -INFINITY;
+#pragma unroll 1
+  for (int b = 0; b < live_blocks; ++b) {
+    float v[4][8];
+    int ix[4][8];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[c][e] = sv[(32 * b + 8 * c + e) * kTileM];
+        ix[c][e] = si[(32 * b + 8 * c + e) * kTileM];
+      }
+    }
+    topk_merge32_desc(v, ix);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        sv[(32 * b + 8 * c + e) * kTileM] = v[c][e];
+        si[(32 * b + 8 * c + e) * kTileM] = ix[c][e];
+      }
+    }
+    if (b == ((k - 1) >> 5)) {  // the block that holds the k-th entry
+      const int at = (k - 1) & 31;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e)
+          if (8 * c + e == at) kth = v[c][e];
+      }
+    }
+  }
+  FBMM_PROF_PHASE(2);
+  return kth;
+}
+
+// Copies the warp's 32 finished lists from the scratch area to the caller's layout
+// (values [row][k] fp32, indices [row][k] int64 with `index_offset` added, empty entries
+// -inf / -1), 32 entries of every row at a time through the warp's staging slots: a lane
+// parks its own row's entries with the column rotated by the slot number, so that both
+// the row-wise writes and the entry-wise reads spread over the banks, and the global
+// stores run along the entries of one row. `rows_valid`: rows of this warp that exist.
+__device__ __forceinline__ void topk_write_out(const float* sv, const int* si, int k, long long index_offset,
+                                               float* lv0, long long* li0, int rows_valid, int2* stg_w) {
+  const int lane = static_cast<int>(lane_id());
+  for (int e0 = 0; e0 < k; e0 += 32) {
+#pragma unroll 8
+    for (int j = 0; j < 32; ++j)
+      stg_w[j * kTileM + ((lane + j) & 31)] = make_int2(__float_as_int(sv[(e0 + j) * kTileM]), si[(e0 + j) * kTileM]);
+    __syncwarp();
+    if (e0 + lane < k) {
+#pragma unroll 4
+      for (int r = 0; r < rows_valid; ++r) {
+        const int2 e = stg_w[lane * kTileM + ((r + lane) & 31)];
+        lv0[static_cast<long long>(r) * k + e0 + lane] = __int_as_float(e.x);
+        li0[static_cast<long long>(r) * k + e0 + lane] = (e.y == kTopkEmpty) ? -1ll : static_cast<long long>(e.y) + index_offset;
+      }
+    }
+    __syncwarp();
+  }
 }
 
 // Shared-memory plan, computed identically on the host (launch size) and in the kernel.
@@ -367,6 +504,7 @@ constexpr int kMaxResidentKBlocks = 4;  // A stays resident up to K = 128
 constexpr uint32_t kPlaneBytes = kTileM * kKBlock * 4;  // one 128 x 32 fp32 plane: 16 KB
 constexpr uint32_t kTopkStageSlots = 32;                // staged candidates per row
 constexpr uint32_t kTopkStageBytes = kTopkStageSlots * kTileM * 8u;
+
 constexpr uint32_t kBarrierBytes = 512;
 constexpr uint32_t kSmemLimit = 232448;  // 227 KB per CTA on sm_100
 
@@ -832,13 +970,21 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       float thr = row_ok ? -INFINITY : INFINITY;
       const uint32_t stg_base = smem_u32(stg + row_in_tile);
       uint32_t stg_slot = stg_base;  // address of this row's next free staging slot
-      bool has_list = false;
-      // list of this warp's first row (rows of a warp are consecutive)
+      bool has_list = false;  // warp-uniform: the lists of this unit have been written
+      // output lists of this warp's first row (rows of a warp are consecutive)
       const long long warp_row0 = (shape.tiles_per_chunk > 0 ? (t0 / shape.tiles_per_chunk) : 0) * epi.topk_chunk_rows +
                                   static_cast<long long>(b) * shape.M + row_base(mb) + static_cast<int>(quarter) * 32;
       float* lv0 = (EPI == kEpiTopk) ? epi.topk_values + warp_row0 * epi.k : nullptr;
       long long* li0 = (EPI == kEpiTopk) ? epi.topk_indices + warp_row0 * epi.k : nullptr;
-      const int2* stg_w = stg + quarter * 32;
+      int2* stg_w = stg + quarter * 32;
+      // running list of this lane's row in the CTA's scratch area
+      float* sv = nullptr;
+      int* si = nullptr;
+      if (EPI == kEpiTopk) {
+        constexpr long long kListEntries = 32ll * TOPK_E * kTileM;
+        sv = epi.topk_scratch + static_cast<long long>(blockIdx.x) * 2 * kListEntries + row_in_tile;
+        si = reinterpret_cast<int*>(sv + kListEntries);
+      }
 
       for (int t = t0; t < t1 && ok; ++t) {
         const int col_tile = t * TILE_N;
@@ -1044,16 +1190,15 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 // at most 8 slots were taken since the last check: merge while 8 are still free
                 const int n_staged = static_cast<int>(stg_slot - stg_base) / kSlotStride;
                 const bool full = n_staged > static_cast<int>(kTopkStageSlots) - 8;
-                const uint32_t need = __ballot_sync(0xffffffffu, full);
-                if (need) {
-                  const uint32_t listed = __ballot_sync(0xffffffffu, has_list);
-                  __syncwarp();
-                  FBMM_PROF_MARK(2, 3, __popc(need));
-                  thr = topk_merge_rows<TOPK_E>(need, listed, n_staged, thr, lv0, li0, epi.k, epi.index_offset,
-                                                stg_w);
+                if (__any_sync(0xffffffffu, full)) {
+                  // every lane merges what its row has staged: the call costs the same for one
+                  // row as for 32
+                  FBMM_PROF_MARK(2, 3, 1);
+                  const float kth = topk_merge_own_rows<TOPK_E>(has_list, n_staged, sv, si, epi.k, stg + row_in_tile);
                   FBMM_PROF_MARK_END(2);
-                  if (full) { stg_slot = stg_base; has_list = true; }
-                  __syncwarp();
+                  if (row_ok) thr = kth;
+                  stg_slot = stg_base;
+                  has_list = true;
                 }
               }
             }
@@ -1075,13 +1220,11 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       } else if (EPI == kEpiTopk) {
         if (ok) {
           const int n_staged = static_cast<int>(stg_slot - stg_base) / (kTileM * 8);
-          const bool pending = row_ok && (n_staged > 0 || !has_list);
-          const uint32_t need = __ballot_sync(0xffffffffu, pending);
-          const uint32_t listed = __ballot_sync(0xffffffffu, has_list);
+          if (__any_sync(0xffffffffu, n_staged > 0) || !has_list)
+            topk_merge_own_rows<TOPK_E>(has_list, n_staged, sv, si, epi.k, stg + row_in_tile);
           __syncwarp();
-          if (need)
-            thr = topk_merge_rows<TOPK_E>(need, listed, n_staged, thr, lv0, li0, epi.k, epi.index_offset,
-                                          stg_w);
+          const int rows_valid = min(32, shape.M - (row_base(mb) + static_cast<int>(quarter) * 32));
+          topk_write_out(sv, si, epi.k, epi.index_offset, lv0, li0, rows_valid, stg_w);
         }
       }
     }

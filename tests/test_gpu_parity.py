@@ -198,6 +198,26 @@ def test_topk_exact_golden(ops, dev, lib):
     device_ok(lib)
 
 
+@pytest.mark.parametrize("kk", [32, 64, 96, 128])
+def test_topk_exact_ties_with_k_a_multiple_of_32(ops, dev, lib, kk):
+    """Small-integer operands: values are exact and ties are everywhere, so the values must
+    equal the oracle's bit for bit and equal values must come lowest index first (the
+    reference's strict comparisons keep the earlier column). k % 32 == 0 takes the
+    one-row-per-lane merge; three row blocks' worth of rows and thousands of columns make
+    every row merge many times, and 203 rows leave a warp with rows past the end."""
+    A, B = R.exact_inputs(2, 203, 24, 2900, seed=400 + kk, lo=-3, hi=3)
+    for dim in (1, 2):
+        v, i = ops["topk"](A.to(dev), B.to(dev), k=kk, dim=dim)
+        C = torch.bmm(A.double(), B.double())
+        if dim == 1:
+            C = C.transpose(1, 2).contiguous()
+        # stable descending sort = larger value first, lower index first among equals
+        order = torch.sort(C, dim=-1, descending=True, stable=True)
+        assert torch.equal(v.cpu().double(), order.values[..., :kk]), dim
+        assert torch.equal(i.cpu(), order.indices[..., :kk]), dim
+    device_ok(lib)
+
+
 def test_topk_short_rows_pad(ops, dev):
     g = load_golden("exact_topk_short")
     A, B, k = f32(g["A"]), f32(g["B"]), int(g["k"])
