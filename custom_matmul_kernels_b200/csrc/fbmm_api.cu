@@ -1,5 +1,6 @@
 // Host side of libfbmm.so: argument validation, tensor-map construction, work
 // decomposition and launches behind the C ABI declared in include/fbmm.h.
+#include <algorithm>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdarg>
@@ -259,20 +260,38 @@ long long operand_span(const Operand& op, int k, int l) {
 // extra read and write of the operand) and the storage has no large gaps.
 bool presplit_worthwhile(const RowProblem& p) {
   if (p.M < 1024 || p.N < 1024) return false;
-  // The column operand streams past every row block. Its hi and lo planes together must
-  // stay L2-sized: the CTAs drift apart over a long sweep, and a stream that L2 cannot
-  // hold is then re-read from HBM per CTA, where doubling it costs more than it saves.
-  if (operand_span(p.b, p.K, p.L) * 8 > 96ll * 1024 * 1024) return false;
   const long long dense_a = static_cast<long long>(p.L) * p.M * p.K, dense_b = static_cast<long long>(p.L) * p.N * p.K;
   return operand_span(p.a, p.K, p.L) <= 2 * dense_a && operand_span(p.b, p.K, p.L) <= 2 * dense_b;
 }
 
+// The column operand streams past every row block. Its hi and lo planes together must stay
+// L2-sized while the CTAs pass over them: over a long sweep the CTAs drift apart, and a
+// stream that L2 cannot hold is then re-read from HBM per CTA, where doubling it costs more
+// than it saves. Wider operands need the sweep cut into column ranges (min_bmm) or paced
+// (top-k with one chunk per row block).
+bool b_planes_fit_l2(const RowProblem& p) { return operand_span(p.b, p.K, p.L) * 8 <= 96ll * 1024 * 1024; }
+
 bool a_stays_resident(int k) { return (k + kKBlock - 1) / kKBlock <= kMaxResidentKBlocks; }
 
-// Room for the lo planes: the column operand always, the row operand only when it streams
-// through the ring (K > 128); a resident row block is split in shared memory.
+// A column operand stored with n contiguous has the K pieces of a column tile one whole row
+// of the operand apart. Once the operand is large, every tile then touches dozens of pages
+// out of a set no TLB holds (measured on a 1 GB operand with K = 256: 134 instead of 223
+// TFLOP/s; from 64 MB up the k-contiguous form is 10-15 % faster). Such an operand is
+// copied, while it is being split anyway, into k-contiguous hi and lo planes.
+bool b_gets_repacked(const RowProblem& p) {
+  return p.b.mn_major && p.L <= 65535 && operand_span(p.b, p.K, p.L) * 4 >= (64ll << 20);
+}
+int repacked_pitch(int k) { return (k + 3) / 4 * 4; }
+size_t repacked_plane_bytes(const RowProblem& p) {
+  return align_up(static_cast<size_t>(p.L) * p.N * repacked_pitch(p.K) * 4, 256);
+}
+
+// Room for the pre-split planes: the column operand's lo plane (or both its planes when it
+// is repacked), and the row operand's lo plane only when it streams through the ring
+// (K > 128); a resident row block is split in shared memory.
 size_t presplit_bytes(const RowProblem& p) {
   const size_t a = a_stays_resident(p.K) ? 0 : align_up(static_cast<size_t>(operand_span(p.a, p.K, p.L)) * 4, 256);
+  if (b_gets_repacked(p)) return a + 2 * repacked_plane_bytes(p);
   return a + align_up(static_cast<size_t>(operand_span(p.b, p.K, p.L)) * 4, 256);
 }
 
@@ -334,7 +353,6 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
   const bool pairs = use_pairs(p.M);
   const int b_box = pairs ? kTileN / 2 : kTileN;  // a CTA of a pair fetches half of each B tile
   if ((rc = make_tensor_map(&ta, p.a, p.K, p.L, kTileM)) != FBMM_OK) return rc;
-  if ((rc = make_tensor_map(&tb, p.b, p.K, p.L, b_box)) != FBMM_OK) return rc;
   const bool presplit = lo_scratch != nullptr && (EPI == kEpiMin || EPI == kEpiTopk);
   if (presplit) {
     const bool a_too = !a_stays_resident(p.K);
@@ -345,17 +363,35 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
     const int threads = 256;
     const int blocks = st.sms * 8;
     if (a_too) fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.a.ptr, a_lo, span_a);
-    fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.b.ptr, b_lo, span_b);
+    Operand oa = p.a, ob_hi = p.b, ob_lo = p.b;
+    if (b_gets_repacked(p)) {
+      // both planes of the column operand, k-contiguous, in the scratch: [hi][lo]
+      const int kp = repacked_pitch(p.K);
+      float* b_hi = b_lo;
+      b_lo = reinterpret_cast<float*>(reinterpret_cast<char*>(b_hi) + repacked_plane_bytes(p));
+      const dim3 grid(static_cast<unsigned>((p.N + 31) / 32), static_cast<unsigned>((kp + 31) / 32), static_cast<unsigned>(p.L));
+      fbmm_split_transpose_kernel<<<grid, dim3(32, 8, 1), 0, stream>>>(p.b.ptr, b_hi, b_lo, p.K, p.N, kp, p.b.ld,
+                                                                       p.L > 1 ? p.b.stride : 0);
+      ob_hi.ptr = b_hi;
+      ob_hi.mn_major = false;
+      ob_hi.ld = kp;
+      ob_hi.stride = static_cast<long long>(p.N) * kp;
+      ob_lo = ob_hi;
+      shape.b_mn = 0;
+    } else {
+      fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.b.ptr, b_lo, span_b);
+    }
+    ob_lo.ptr = b_lo;
     FBMM_CUDA(cudaGetLastError());
-    Operand oa = p.a, ob = p.b;
-    ob.ptr = b_lo;
     ta_lo = ta;
     if (a_too) {
       oa.ptr = a_lo;
       if ((rc = make_tensor_map(&ta_lo, oa, p.K, p.L, kTileM)) != FBMM_OK) return rc;
     }
-    if ((rc = make_tensor_map(&tb_lo, ob, p.K, p.L, b_box)) != FBMM_OK) return rc;
+    if ((rc = make_tensor_map(&tb, ob_hi, p.K, p.L, b_box)) != FBMM_OK) return rc;
+    if ((rc = make_tensor_map(&tb_lo, ob_lo, p.K, p.L, b_box)) != FBMM_OK) return rc;
   } else {
+    if ((rc = make_tensor_map(&tb, p.b, p.K, p.L, b_box)) != FBMM_OK) return rc;
     ta_lo = ta;
     tb_lo = tb;
   }
@@ -530,7 +566,7 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   // room behind the op's own scratch for the lo planes? then the operands are split once up front
   void* lo_scratch = nullptr;
   const size_t lo_off = align_up(need, 256);
-  if (presplit_worthwhile(p) && workspace_bytes >= lo_off + presplit_bytes(p)) {
+  if (presplit_worthwhile(p) && (b_planes_fit_l2(p) || p.L == 1) && workspace_bytes >= lo_off + presplit_bytes(p)) {
     lo_scratch = static_cast<char*>(workspace) + lo_off;
     // B's two planes should stay in L2 while every row block passes over them. What L2
     // keeps of data that all SMs share is about half its size, so wider B is swept in
@@ -582,8 +618,23 @@ static size_t topk_scratch_bytes(int sms, int topk) {
   return static_cast<size_t>(sms) * list_slots * kTileM * 8;
 }
 
+// Pacing of a one-chunk sweep (GemmShape::pace_tiles): ranges of about 16 MB of the column
+// operand's two planes, and one counter per range and per unit a CTA works through.
+struct PacePlan {
+  int tiles;
+  size_t count_bytes;
+};
+static PacePlan pace_plan(int l, int m_blocks, int n_tiles, int k, int workers) {
+  const long long tile_bytes = 2ll * kTileN * ((k + kKBlock - 1) / kKBlock * kKBlock) * 4;
+  PacePlan pp;
+  pp.tiles = static_cast<int>(std::max(1ll, (16ll << 20) / tile_bytes));
+  const long long ranges = (n_tiles + pp.tiles - 1) / pp.tiles;
+  const long long per_cta = (static_cast<long long>(l) * m_blocks + workers - 1) / workers;
+  pp.count_bytes = align_up(static_cast<size_t>(per_cta * ranges) * sizeof(unsigned int), 256);
+  return pp;
+}
+
 size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim, int distance) {
-  (void)k;
   if (l <= 0 || m <= 0 || n <= 0 || topk <= 0) return 0;
   const int rows_pb = dim == 1 ? n : m, cols = dim == 1 ? m : n;
   int n_chunks, tpc;
@@ -595,7 +646,12 @@ size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int d
   }
   if (distance == FBMM_DIST_L2)
     need = align_up(need, 256) + align_up(static_cast<size_t>(l) * m * 4, 256) + align_up(static_cast<size_t>(l) * n * 4, 256);
-  return align_up(need, 256) + topk_scratch_bytes(sm_count_or_default(), topk);
+  need = align_up(need, 256) + topk_scratch_bytes(sm_count_or_default(), topk);
+  if (n_chunks == 1) {
+    const int sms = sm_count_or_default();
+    need += pace_plan(l, (rows_pb + kTileM - 1) / kTileM, (cols + kTileN - 1) / kTileN, k, sms).count_bytes;
+  }
+  return need;
 }
 
 int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long* cand_indices, int groups,
@@ -664,9 +720,28 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
     e.topk_scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + own);
     own = need;
   }
+  // One chunk per row block and a column operand wider than L2: the sweep can be paced,
+  // which is what makes pre-split planes of any size affordable.
+  const bool can_pace = s.n_chunks == 1 && !use_pairs(p.M);
+  unsigned int* pace_counts = nullptr;
+  PacePlan pp{};
+  if (s.n_chunks == 1) {
+    pp = pace_plan(l, (p.M + kTileM - 1) / kTileM, s.n_tiles, p.K, st->sms);
+    if (workspace_bytes < own + pp.count_bytes)
+      return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", own + pp.count_bytes, workspace_bytes);
+    pace_counts = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + own);
+    own += pp.count_bytes;
+  }
   void* lo_scratch = nullptr;
-  if (presplit_worthwhile(p) && workspace_bytes >= own + presplit_bytes(p))
+  if (presplit_worthwhile(p) && (b_planes_fit_l2(p) || can_pace) && workspace_bytes >= own + presplit_bytes(p)) {
     lo_scratch = static_cast<char*>(workspace) + own;
+    if (!b_planes_fit_l2(p)) {
+      s.pace_tiles = pp.tiles;
+      s.pace_slack = 2;
+      s.pace_counts = pace_counts;
+      FBMM_CUDA(cudaMemsetAsync(pace_counts, 0, pp.count_bytes, stream));
+    }
+  }
   if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch);  // list slots per lane
   else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e, lo_scratch);
   if (rc != FBMM_OK) return rc;

@@ -34,6 +34,7 @@ constexpr int kNumThreads = 320;
 constexpr int kSplitThreads = 128;
 constexpr int kEpiThreads = 128;
 constexpr int kTmemCols = 512;
+constexpr long long kPaceWaitCycles = 4000000;  // longest a CTA holds back for the others (~2 ms)
 
 enum EpilogueKind { kEpiStore = 0, kEpiMask = 1, kEpiMin = 2, kEpiTopk = 3 };
 
@@ -88,6 +89,16 @@ struct GemmShape {
   int chunk_major;      // unit order: 0 = chunks of one row block are consecutive,
                         // 1 = all row blocks of chunk 0 first, then chunk 1, ... (keeps the
                         // CTAs inside one L2-sized column range of B at a time)
+  // Pacing of long sweeps (0 / null: off). A unit's column tiles are counted off in ranges of
+  // `pace_tiles`; range number g of a CTA (counted over all its units) is not started before
+  // every CTA has requested all tiles of its range g - 2. The CTAs then read the same
+  // L2-sized part of B at about the same time instead of drifting apart over a long sweep,
+  // after which each would fetch B from HBM for itself. Only a hint: a CTA that has waited
+  // long enough goes on regardless. pace_counts[g] counts the CTAs done with range g (zeroed
+  // by the host); needs n_chunks == 1 and one CTA per unit.
+  int pace_tiles;
+  int pace_slack;  // ranges a CTA may be ahead of the slowest one (>= 1)
+  unsigned int* pace_counts;
 };
 
 struct EpiArgs {
@@ -738,12 +749,27 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       bool ok = true;
       FBMM_PROF_DECL;
       const long long prof_start = clock64();
+      long long pace_seq = 0;  // number of this CTA's next range
+      const long long pace_ranges = shape.pace_tiles > 0 ? (shape.n_tiles + shape.pace_tiles - 1) / shape.pace_tiles : 0;
       for (long long u = unit_first; u < units && ok; u += unit_step) {
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range(b, mb, t0, t1, first, last)) continue;
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
+          if (shape.pace_tiles > 0 && (t - t0) % shape.pace_tiles == 0) {
+            if (pace_seq > 0) atomicAdd(shape.pace_counts + pace_seq - 1, 1u);  // the range before is requested
+            if (pace_seq >= shape.pace_slack) {
+              // CTAs that have a unit of the ordinal the awaited range belongs to
+              const long long g = pace_seq - shape.pace_slack;
+              const long long ahead = units - (g / pace_ranges) * unit_step;
+              const unsigned int expected = static_cast<unsigned int>(ahead < unit_step ? ahead : unit_step);
+              const volatile unsigned int* cnt = shape.pace_counts + g;
+              const long long w0 = clock64();
+              while (*cnt < expected && clock64() - w0 < kPaceWaitCycles) __nanosleep(256);
+            }
+            ++pace_seq;
+          }
           for (int kb = 0; kb < kblocks; ++kb) {
             if (A_RES && t == first) {
               // the row block's A k-block, loaded once per unit as soon as the previous
@@ -776,6 +802,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         a_phase ^= 1u;
       }
+      // the last range counts too: CTAs with one more unit wait for it
+      if (shape.pace_tiles > 0 && pace_seq > 0) atomicAdd(shape.pace_counts + pace_seq - 1, 1u);
 #ifdef FBMM_PROFILE
       prof_acc_[1] = clock64() - prof_start;
 #endif
@@ -1255,6 +1283,31 @@ __global__ void fbmm_split_lo_kernel(const float* __restrict__ src, float* __res
     lo4[i] = make_float4(split_lo(x.x), split_lo(x.y), split_lo(x.z), split_lo(x.w));
   }
   if (tid < (count & 3)) lo[4 * count4 + tid] = split_lo(src[4 * count4 + tid]);
+}
+
+// hi and lo planes of an operand stored [l][k][n] (n contiguous, pitch `ld`), written
+// transposed as [l][n][kp] (k contiguous, kp >= K a multiple of 4, zero beyond K): hi is a
+// copy, lo = x - tf32(x). A column tile of a very wide operand then is one contiguous piece
+// of memory instead of K pieces a whole row of the operand apart. Block 32 x 8, tile 32 x 32.
+__global__ void fbmm_split_transpose_kernel(const float* __restrict__ src, float* __restrict__ hi,
+                                            float* __restrict__ lo, int K, int N, int kp, long long ld, long long stride) {
+  __shared__ float tile[32][33];
+  const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  const long long l = blockIdx.z;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int k = k0 + j, n = n0 + static_cast<int>(threadIdx.x);
+    tile[j][threadIdx.x] = (k < K && n < N) ? src[l * stride + static_cast<long long>(k) * ld + n] : 0.f;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int n = n0 + j, k = k0 + static_cast<int>(threadIdx.x);
+    if (n < N && k < kp) {
+      const float x = tile[threadIdx.x][j];
+      const long long at = (l * N + n) * kp + k;
+      hi[at] = x;
+      lo[at] = split_lo(x);
+    }
+  }
 }
 
 // Squared norms of the rows of an operand: out[l][r] = sum_k x[l][r][k]^2. `ld` is the pitch

@@ -76,13 +76,15 @@ def test_workspace_queries(lib):
     assert lib.fbmm_min_bmm_workspace_bytes(2, 100, 300, 64, 1, 0) == 2 * 300 * 8
     # l2 distance adds room for the squared norms of both operands
     assert lib.fbmm_min_bmm_workspace_bytes(1, 256, 512, 64, 2, 1) == 256 * 8 + 256 * 4 + 512 * 4
-    # many row blocks: one column chunk, only the running lists of the units in flight
-    # (per SM 128 rows x 64 or 128 list slots x 8 bytes; 148 SMs assumed without a device)
-    lists64 = lib.fbmm_topk_bmm_workspace_bytes(1, 1 << 20, 1 << 20, 256, 64, 2, 0)
-    lists128 = lib.fbmm_topk_bmm_workspace_bytes(1, 1 << 20, 1 << 20, 256, 100, 2, 0)
-    assert lists64 > 0 and lists64 % (128 * 64 * 8) == 0 and lists128 == 2 * lists64
+    # many row blocks: one column chunk; the running lists of the units in flight (per SM
+    # 128 rows x 64 or 128 list slots x 8 bytes) and a few KB of sweep-pacing counters
+    sms = 148  # assumed by the library without a device; a B200 has as many
+    w64 = lib.fbmm_topk_bmm_workspace_bytes(1, 1 << 20, 1 << 20, 256, 64, 2, 0)
+    w128 = lib.fbmm_topk_bmm_workspace_bytes(1, 1 << 20, 1 << 20, 256, 100, 2, 0)
+    lists64 = sms * 128 * 64 * 8
+    assert lists64 < w64 < lists64 + (1 << 20) and w128 - w64 == lists64
     # few row blocks: per-chunk candidate lists on top
-    assert lib.fbmm_topk_bmm_workspace_bytes(1, 128, 1 << 16, 64, 64, 2, 0) > lists64
+    assert lib.fbmm_topk_bmm_workspace_bytes(1, 128, 1 << 16, 64, 64, 2, 0) > w64
 
 
 def test_wrappers_reject_bad_inputs_on_cpu():

@@ -339,6 +339,73 @@ def test_presplit_scratch_gives_identical_bits(dev, lib):
     assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
 
 
+def test_topk_and_min_with_pre_split_planes_wider_than_l2(dev, lib):
+    """A column operand whose hi and lo planes (2 x 51 MB) exceed what L2 keeps: top-k sweeps
+    it paced (every CTA holds back until the others have asked for the range before last),
+    min sweeps it in column ranges. Same bits as without pre-split planes, and the oracle's
+    answer on a sample of rows (the full product is too much for the CPU side of a test)."""
+    m, k, n = 148 * 128 + 60, 64, 200000
+    g = torch.Generator().manual_seed(77)
+    A = torch.randn(1, m, k, generator=g).to(dev)
+    B = torch.randn(1, k, n, generator=g).to(dev)
+    stream = torch.cuda.current_stream().cuda_stream
+    extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, ord("n"), k, m * k, ord("n"), n, k * n)
+    assert extra >= k * n * 4
+    outs = []
+    for use_extra in (False, True):
+        own = (lib.fbmm_min_bmm_workspace_bytes(1, m, n, k, 2, 0) + 255) // 256 * 256
+        nbytes = own + (extra if use_extra else 0)
+        ws = torch.empty(nbytes, device=dev, dtype=torch.uint8)
+        v = torch.empty(1, m, device=dev)
+        i = torch.empty(1, m, device=dev, dtype=torch.int64)
+        rc = lib.fbmm_min_bmm_f32(stream, A.data_ptr(), ord("n"), k, m * k, B.data_ptr(), ord("n"), n, k * n,
+                                  v.data_ptr(), i.data_ptr(), 1, m, n, k, 2, 0, ws.data_ptr(), nbytes)
+        assert rc == 0, lib.fbmm_last_error()
+        own_t = (lib.fbmm_topk_bmm_workspace_bytes(1, m, n, k, 32, 2, 0) + 255) // 256 * 256
+        nb_t = own_t + (extra if use_extra else 0)
+        ws_t = torch.empty(nb_t, device=dev, dtype=torch.uint8)
+        tv = torch.empty(1, m, 32, device=dev)
+        ti = torch.empty(1, m, 32, device=dev, dtype=torch.int64)
+        rc = lib.fbmm_topk_bmm_f32(stream, A.data_ptr(), ord("n"), k, m * k, B.data_ptr(), ord("n"), n, k * n,
+                                   tv.data_ptr(), ti.data_ptr(), 1, m, n, k, 32, 2, 0, 0, ws_t.data_ptr(), nb_t)
+        assert rc == 0, lib.fbmm_last_error()
+        torch.cuda.synchronize()
+        outs.append((v, i, tv, ti))
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    rows = torch.cat([torch.arange(0, 160), torch.arange(9000, 9100), torch.arange(m - 130, m)])
+    As, Bc = A.cpu()[:, rows], B.cpu()
+    R.check_min(outs[1][0][:, rows], outs[1][1][:, rows], As, Bc, 2)
+    R.check_topk(outs[1][2][:, rows], outs[1][3][:, rows], As, Bc, 32, 2)
+    assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
+
+
+def test_topk_and_min_on_a_repacked_column_operand(ops, dev, lib):
+    """B stored [k][n] with a million columns (256 MB; the rewrite starts at 64 MB): its planes
+    are rewritten k-contiguous before the sweep. Oracle on a sample of rows, and the same bits as with B
+    handed over k-contiguous by the caller (layout 't'), where nothing is repacked."""
+    m, k, n = 148 * 128, 64, 1 << 20
+    g = torch.Generator().manual_seed(78)
+    A = torch.randn(1, m, k, generator=g).to(dev)
+    Bc = torch.randn(1, k, n, generator=g)
+    B = Bc.to(dev)
+    Bt = B.transpose(1, 2).contiguous().transpose(1, 2)  # same values, stored [n][k]
+    tk, mn = ops["topk"], ops["min"]
+    extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, ord("n"), k, m * k, ord("n"), n, k * n)
+    assert extra >= 2 * n * k * 4  # both planes of B
+    tv, ti = tk(A, B, k=32, dim=2)
+    tv2, ti2 = tk(A, Bt, k=32, dim=2)
+    mv, mi = mn(A, B, dim=2)
+    mv2, mi2 = mn(A, Bt, dim=2)
+    assert torch.equal(tv, tv2) and torch.equal(ti, ti2)
+    assert torch.equal(mv, mv2) and torch.equal(mi, mi2)
+    rows = torch.cat([torch.arange(0, 40), torch.arange(m - 24, m)])
+    As = A.cpu()[:, rows]
+    R.check_min(mv[:, rows], mi[:, rows], As, Bc, 2)
+    R.check_topk(tv[:, rows], ti[:, rows], As, Bc, 32, 2)
+    assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
+
+
 # ----------------------------------------------------------------------------- l2 distance
 @pytest.mark.parametrize("shape", [(1, 200, 40, 300), (2, 130, 64, 257), (1, 1100, 96, 1300), (1, 64, 200, 520)])
 def test_min_and_topk_l2_distance(dev, lib, shape):
