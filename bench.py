@@ -188,6 +188,10 @@ class Workload:
         else:
             self.op = TopkBMMCUDA()
             self.kernels_per_step = 1 + (1 if world > 1 else 0)  # + candidate merge
+            l_, m_, k_ = self.A.shape
+            n_ = self.B.shape[2]
+            if self.op.lib.fbmm_presplit_workspace_bytes(l_, m_, n_, k_, ord("n"), k_, m_ * k_, ord("n"), n_, k_ * n_):
+                self.kernels_per_step += 2 if k_ > 128 else 1  # plane passes over B and, when it streams, A
         self.out_host = None
 
     def run(self, A, B, masks=None):

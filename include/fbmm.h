@@ -122,12 +122,13 @@ int fbmm_min_bmm_f32_noalloc(void* stream,
 /* Optional extra scratch for fbmm_min_bmm_f32 and fbmm_topk_bmm_f32. The kernels form every
  * fp32 product from three tf32 products of (hi, lo) operand planes; normally the lo planes
  * are produced in shared memory tile by tile. When the caller's workspace has this many
- * bytes beyond the op's own need (rounded up to 256), the lo planes of the operands that
+ * bytes beyond the op's own need (rounded up to 256), the planes of the operands that
  * stream through shared memory (the column operand; for k > 128 the row operand too) are
- * computed once into that room instead, which pays when every tile is fetched many times. Returns 0
+ * computed once into that room instead, which pays when every tile is fetched many times.
+ * A column operand of 64 MB or more that is stored with n contiguous gets both its planes
+ * written there k-contiguous (so this query can exceed the operands' own size). Returns 0
  * for shapes where it would not be used (fewer than 1024 rows or columns, or storage with
- * large gaps, or a column operand whose two planes exceed 96 MB and would fall out of L2).
- * Same answers either way. No reference counterpart (its kernels multiply in
+ * large gaps). Same answers either way. No reference counterpart (its kernels multiply in
  * fp32 on the CUDA cores, kernels/bmm_helpers.cu:20-26). */
 size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k,
                                      int a_layout, long long lda, long long stride_a,
@@ -140,7 +141,10 @@ size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k,
  * 0 < topk <= 128 (topkbmm.py:104). Outputs are contiguous [.., topk] (the reference
  * returns [:, :, :k] views of 128-wide buffers, topkbmm.py:150-151). If fewer than topk
  * entries exist the tail is -inf / -1 (kernels/topkbmm.cu:277-278). `index_offset` is
- * added to every index written (used when B holds a column shard). */
+ * added to every index written (used when B holds a column shard). The workspace is always
+ * needed: it holds the running lists of the row blocks in flight (the reference keeps them
+ * in the 128-wide output buffers under a spin lock, kernels/topkbmm.cu:13-47), a few KB of
+ * counters, and per-chunk lists when a row block's columns are split over several CTAs. */
 size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim, int distance);
 int fbmm_topk_bmm_f32(void* stream,
                       const float* A, int a_layout, long long lda, long long stride_a,
