@@ -303,10 +303,10 @@ def test_c_abi_min_workspace_too_small(dev, lib):
 def test_presplit_scratch_gives_identical_bits(dev, lib):
     """With room for pre-split lo planes in the workspace the kernels skip their in-kernel
     splitter; the planes hold the same values either way, so the outputs must not differ
-    in a single bit (min with K <= 128, top-k with K > 128)."""
+    in a single bit (min and top-k with K <= 128 and K > 128)."""
     g = torch.Generator().manual_seed(31)
     stream = torch.cuda.current_stream().cuda_stream
-    for (m, k, n) in [(1100, 96, 1300), (1024, 160, 1536)]:
+    for (m, k, n) in [(1100, 96, 1300), (1024, 160, 1536), (1280, 128, 1100)]:
         A = torch.randn(1, m, k, generator=g).to(dev)
         B = torch.randn(1, k, n, generator=g).to(dev)
         extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, ord("n"), k, m * k, ord("n"), n, k * n)
