@@ -1195,38 +1195,50 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else {
             // top-k: only values that beat the row's current k-th best are staged; the
             // stage is merged into the row's list before it can overflow. Groups of 8
-            // columns in which no row of the warp has a candidate are skipped outright.
+            // columns in which no row of the warp has a candidate are skipped outright
+            // (a threshold raised by a merge inside the chunk only makes the group test
+            // conservative: the values themselves are compared with the current one).
             constexpr int kSlotStride = kTileM * 8;
             if (col0 + 32 > shape.N) {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (col0 + j >= shape.N) v[j] = -INFINITY;  // never greater than a threshold
             }
+            // which groups of 8 columns hold, in any row of the warp, a value above that row's
+            // threshold: one OR-reduction over the warp answers for all four groups
+            uint32_t mine = 0;
 #pragma unroll
-            for (int j0 = 0; j0 < 32; j0 += 8) {
+            for (int g = 0; g < 4; ++g) {
+              const int j0 = 8 * g;
               const float mx = fmaxf(fmaxf(fmaxf(v[j0], v[j0 + 1]), fmaxf(v[j0 + 2], v[j0 + 3])),
                                      fmaxf(fmaxf(v[j0 + 4], v[j0 + 5]), fmaxf(v[j0 + 6], v[j0 + 7])));
-              if (__any_sync(0xffffffffu, mx > thr)) {
-                uint32_t hit = 0;
+              mine |= (mx > thr ? 1u : 0u) << g;
+            }
+            const uint32_t groups = __reduce_or_sync(0xffffffffu, mine);
+            if (groups != 0) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) hit |= (v[j0 + j] > thr ? 1u : 0u) << j;
+              for (int g = 0; g < 4; ++g) {
+                if ((groups >> g) & 1u) {  // warp-uniform
+                  const int j0 = 8 * g;
 #pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  topk_stage_if((hit >> j) & 1u, stg_slot + __popc(hit & ((1u << j) - 1u)) * kSlotStride, v[j0 + j],
-                                col0 + j0 + j);
-                stg_slot += __popc(hit) * kSlotStride;
-                // at most 8 slots were taken since the last check: merge while 8 are still free
-                const int n_staged = static_cast<int>(stg_slot - stg_base) / kSlotStride;
-                const bool full = n_staged > static_cast<int>(kTopkStageSlots) - 8;
-                if (__any_sync(0xffffffffu, full)) {
-                  // every lane merges what its row has staged: the call costs the same for one
-                  // row as for 32
-                  FBMM_PROF_MARK(2, 3, 1);
-                  const float kth = topk_merge_own_rows<TOPK_E>(has_list, n_staged, sv, si, epi.k, stg + row_in_tile);
-                  FBMM_PROF_MARK_END(2);
-                  if (row_ok) thr = kth;
-                  stg_slot = stg_base;
-                  has_list = true;
+                  for (int j = 0; j < 8; ++j) {
+                    const uint32_t hit = v[j0 + j] > thr ? 1u : 0u;
+                    topk_stage_if(hit, stg_slot, v[j0 + j], col0 + j0 + j);
+                    stg_slot += hit * kSlotStride;
+                  }
+                  // at most 8 slots were taken since the last check: merge while 8 are still free
+                  const int n_staged = static_cast<int>(stg_slot - stg_base) / kSlotStride;
+                  const bool full = n_staged > static_cast<int>(kTopkStageSlots) - 8;
+                  if (__any_sync(0xffffffffu, full)) {
+                    // every lane merges what its row has staged: the call costs the same for
+                    // one row as for 32
+                    FBMM_PROF_MARK(2, 3, 1);
+                    const float kth = topk_merge_own_rows<TOPK_E>(has_list, n_staged, sv, si, epi.k, stg + row_in_tile);
+                    FBMM_PROF_MARK_END(2);
+                    if (row_ok) thr = kth;
+                    stg_slot = stg_base;
+                    has_list = true;
+                  }
                 }
               }
             }
