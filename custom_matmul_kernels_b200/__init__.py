@@ -8,5 +8,6 @@ from .bmm import BMMCUDA
 from .mbmm import MBMMCUDA, make_masks
 from .minbmm import MinBMMCUDA
 from .topkbmm import TopkBMMCUDA
+from .kmeans import KMeansCUDA
 
-__all__ = ["BMMCUDA", "MBMMCUDA", "MinBMMCUDA", "TopkBMMCUDA", "make_masks"]
+__all__ = ["BMMCUDA", "MBMMCUDA", "MinBMMCUDA", "TopkBMMCUDA", "KMeansCUDA", "make_masks"]

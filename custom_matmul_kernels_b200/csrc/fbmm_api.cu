@@ -826,6 +826,57 @@ extern "C" int fbmm_topk_merge_f32(void* stream, const float* cand_values, const
 }
 
 // ---------------------------------------------------------------------------------------
+// k-means centroid update (the consumer of min_bmm with the l2 distance)
+// ---------------------------------------------------------------------------------------
+extern "C" size_t fbmm_kmeans_update_workspace_bytes(int k, int d) {
+  if (k <= 0 || d <= 0) return 0;
+  return align_up(static_cast<size_t>(k) * d * 4, 256) + align_up(static_cast<size_t>(k) * 4, 256);
+}
+
+extern "C" int fbmm_kmeans_update_f32(void* stream_, const float* X, long long ldx, const long long* assignment,
+                                      long long n, int d, int k, float* centroids, long long ldc, float* counts_out,
+                                      void* workspace, size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (X == nullptr || assignment == nullptr || centroids == nullptr) return fail(FBMM_ERR_INVALID, "a pointer is null");
+  if (n <= 0 || d <= 0 || k <= 0) return fail(FBMM_ERR_INVALID, "n, d, k must be positive, got %lld %d %d", n, d, k);
+  if (ldx < d || ldc < d) return fail(FBMM_ERR_INVALID, "a pitch is smaller than d");
+  const size_t need = fbmm_kmeans_update_workspace_bytes(k, d);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(FBMM_ERR_WORKSPACE, "kmeans_update needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  DeviceState* st;
+  int rc;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  float* sums = static_cast<float*>(workspace);
+  float* counts = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(static_cast<size_t>(k) * d * 4, 256));
+  FBMM_CUDA(cudaMemsetAsync(workspace, 0, need, stream));
+  const int threads = 256;
+  const size_t part_bytes = (static_cast<size_t>(k) * d + k) * sizeof(float);
+  if (part_bytes <= 96 * 1024 && n >= 65536) {
+    // few clusters: per-CTA partial sums in shared memory, two CTAs per SM
+    static std::mutex attr_mu;
+    {
+      std::lock_guard<std::mutex> g(attr_mu);
+      FBMM_CUDA(cudaFuncSetAttribute(fbmm::fbmm_kmeans_accumulate_smem_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024));
+    }
+    fbmm::fbmm_kmeans_accumulate_smem_kernel<<<static_cast<unsigned>(st->sms * 2), 512, part_bytes, stream>>>(
+        X, ldx, assignment, n, d, k, sums, counts);
+  } else {
+    const long long want = (n * 32 + threads - 1) / threads;
+    const long long cap = static_cast<long long>(st->sms) * 32;
+    fbmm::fbmm_kmeans_accumulate_kernel<<<static_cast<unsigned>(want < cap ? want : cap), threads, 0, stream>>>(
+        X, ldx, assignment, n, d, k, sums, counts);
+  }
+  const long long total = static_cast<long long>(k) * d;
+  fbmm::fbmm_kmeans_finalize_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(
+      sums, counts, centroids, ldc, d, total);
+  if (counts_out != nullptr)
+    FBMM_CUDA(cudaMemcpyAsync(counts_out, counts, static_cast<size_t>(k) * 4, cudaMemcpyDeviceToDevice, stream));
+  FBMM_CUDA(cudaGetLastError());
+  return FBMM_OK;
+}
+
+// ---------------------------------------------------------------------------------------
 // min_bmm without caller scratch and without any allocation
 // ---------------------------------------------------------------------------------------
 // Some hosts that embed this library through the C ABI cannot allocate device memory at

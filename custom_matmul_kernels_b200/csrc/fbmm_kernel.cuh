@@ -1366,4 +1366,65 @@ __global__ void fbmm_min_finalize_kernel(const unsigned long long* __restrict__ 
   indices[i] = static_cast<long long>(static_cast<uint32_t>(key & 0xffffffffu));
 }
 
+// k-means centroid update, the step after min_bmm with the l2 distance has assigned every
+// point to its nearest centroid: sums[c][:] += X[i][:] and counts[c] += 1 for c = assign[i].
+// One warp per point; the additions are fire-and-forget reductions that resolve in L2,
+// where the k x d sums live. Summation order, and with it the last bits of the result,
+// varies from run to run. Points with an assignment outside [0, k) are skipped.
+__global__ void fbmm_kmeans_accumulate_kernel(const float* __restrict__ x, long long ldx,
+                                              const long long* __restrict__ assign, long long n, int d, int k,
+                                              float* __restrict__ sums, float* __restrict__ counts) {
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int lane = static_cast<int>(threadIdx.x & 31u);
+  for (long long i = warp; i < n; i += warps) {
+    const long long c = assign[i];
+    if (c < 0 || c >= k) continue;
+    const float* row = x + i * ldx;
+    float* dst = sums + c * d;
+    for (int j = lane; j < d; j += 32) atomicAdd(dst + j, row[j]);
+    if (lane == 0) atomicAdd(counts + c, 1.f);
+  }
+}
+
+// The same with the k x d sums and the k counts of a CTA's points first gathered in shared
+// memory (dynamic: (k * d + k) floats) and added to the global ones once at the end. With
+// few clusters every point of the plain kernel lands on the same few lines in L2; here the
+// contended additions stay on chip.
+__global__ void fbmm_kmeans_accumulate_smem_kernel(const float* __restrict__ x, long long ldx,
+                                                   const long long* __restrict__ assign, long long n, int d, int k,
+                                                   float* __restrict__ sums, float* __restrict__ counts) {
+  extern __shared__ float part[];  // [k * d] sums, then [k] counts
+  const int cells = k * d + k;
+  for (int i = threadIdx.x; i < cells; i += blockDim.x) part[i] = 0.f;
+  __syncthreads();
+  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const int lane = static_cast<int>(threadIdx.x & 31u);
+  for (long long i = warp; i < n; i += warps) {
+    const long long c = assign[i];
+    if (c < 0 || c >= k) continue;
+    const float* row = x + i * ldx;
+    float* dst = part + c * d;
+    for (int j = lane; j < d; j += 32) atomicAdd(dst + j, row[j]);
+    if (lane == 0) atomicAdd(part + k * d + c, 1.f);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < cells; i += blockDim.x) {
+    const float v = part[i];
+    if (v != 0.f) atomicAdd(i < k * d ? sums + i : counts + (i - k * d), v);
+  }
+}
+
+// centroids[c][:] = sums[c][:] / counts[c]; a centroid no point chose keeps its old place.
+__global__ void fbmm_kmeans_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ counts,
+                                            float* __restrict__ centroids, long long ldc, int d, long long total) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long c = i / d;
+  const int j = static_cast<int>(i - c * d);
+  const float cnt = counts[c];
+  if (cnt > 0.f) centroids[c * ldc + j] = sums[i] / cnt;
+}
+
 }  // namespace fbmm

@@ -66,6 +66,9 @@ SIGNATURES = {
     "fbmm_topk_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                           _c_int, _c_int, _c_ll, _c_ptr, _c_size]),
     "fbmm_topk_merge_f32": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr]),
+    "fbmm_kmeans_update_workspace_bytes": (_c_size, [_c_int, _c_int]),
+    "fbmm_kmeans_update_f32": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr, _c_ll, _c_ptr,
+                                        _c_ptr, _c_size]),
 }
 
 _lib = None

@@ -163,6 +163,19 @@ int fbmm_topk_merge_f32(void* stream,
                         int groups, long long rows, int topk,
                         float* out_values, long long* out_indices);
 
+/* k-means centroid update, the step that consumes min_bmm with FBMM_DIST_L2 (points as A,
+ * centroids as the columns of B, dim = 2: `assignment` is its index output). For every
+ * centroid c that at least one point chose, centroids[c][:] becomes the mean of those
+ * points; the others are left as they are. X is [n][d] with pitch ldx, centroids [k][d] with
+ * pitch ldc, assignment [n] int64 (entries outside [0, k) are skipped); counts_out (or null)
+ * receives the k cluster sizes as fp32. Sums are formed with floating-point atomics, so the
+ * last bits depend on the order the hardware happens to take. The reference has no such
+ * kernel: it stops at the assignment (minbmm.py:78-157). */
+size_t fbmm_kmeans_update_workspace_bytes(int k, int d);
+int fbmm_kmeans_update_f32(void* stream, const float* X, long long ldx, const long long* assignment,
+                           long long n, int d, int k, float* centroids, long long ldc, float* counts_out,
+                           void* workspace, size_t workspace_bytes);
+
 #ifdef __cplusplus
 }
 #endif

@@ -288,6 +288,31 @@ def exact_inputs(l, m, k, n, seed, lo=-8, hi=8):
 
 
 # --------------------------------------------------------------------------------------
+# k-means step (the consumer of min_bmm with the l2 distance)
+# --------------------------------------------------------------------------------------
+
+
+def kmeans_assign(X, centroids):
+    """Nearest centroid by squared Euclidean distance, lowest index on ties: what
+    MinBMMCUDA(distance="l2") returns for points X [n,d] against centroids [k,d]."""
+    d2 = ((X.double()[:, None, :] - centroids.double()[None, :, :]) ** 2).sum(-1)
+    v, i = d2.min(dim=1)
+    return v, i
+
+
+def kmeans_update(X, assignment, centroids):
+    """Mean of the points of every cluster (fp64 sums); empty clusters keep their centroid."""
+    k, d = centroids.shape
+    sums = torch.zeros(k, d, dtype=torch.float64)
+    sums.index_add_(0, assignment, X.double())
+    counts = torch.bincount(assignment, minlength=k).double()
+    out = centroids.double().clone()
+    live = counts > 0
+    out[live] = sums[live] / counts[live, None]
+    return out, counts
+
+
+# --------------------------------------------------------------------------------------
 # timed CPU arm (reference semantics on the host cores)
 # --------------------------------------------------------------------------------------
 

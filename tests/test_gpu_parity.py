@@ -406,6 +406,51 @@ def test_topk_and_min_on_a_repacked_column_operand(ops, dev, lib):
     assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
 
 
+# ----------------------------------------------------------------------------- k-means consumer
+def test_kmeans_step_and_fit(dev, lib):
+    """assign = min_bmm with the l2 distance, update = fbmm_kmeans_update_f32. One step is
+    checked against the oracle (fp64 sums; an empty cluster keeps its centroid), a short
+    fit must not increase the summed distance from one iteration to the next."""
+    from custom_matmul_kernels_b200 import KMeansCUDA
+    g = torch.Generator().manual_seed(5)
+    n, d, k = 5000, 48, 37
+    blobs = torch.randn(k - 1, d, generator=g) * 4
+    X = blobs[torch.randint(0, k - 1, (n,), generator=g)] + torch.randn(n, d, generator=g) * 0.5
+    C0 = torch.cat([X[:k - 1].clone(), torch.full((1, d), 1e3)])  # the last centroid attracts nobody
+    km = KMeansCUDA()
+    dist, idx = km.assign(X.to(dev), C0.to(dev))
+    want_v, want_i = R.kmeans_assign(X, C0)
+    assert float((dist.cpu().double() - want_v).abs().max()) <= 1e-4 + 1e-5 * float(want_v.abs().max())
+    near = (idx.cpu() != want_i)
+    if bool(near.any()):  # only where two centroids are equally near within tolerance
+        d2 = ((X.double()[near][:, None, :] - C0.double()[None]) ** 2).sum(-1)
+        got = d2.gather(1, idx.cpu()[near][:, None])[:, 0]
+        assert bool(((got - want_v[near]).abs() <= 1e-4 + 1e-5 * want_v[near].abs()).all())
+    newc, counts = km.update(X.to(dev), idx, C0.to(dev))
+    want_c, want_n = R.kmeans_update(X, idx.cpu(), C0)
+    assert torch.equal(counts.cpu().double(), want_n)
+    assert float(want_n[-1]) == 0 and torch.equal(newc.cpu()[-1], C0[-1])
+    assert float((newc.cpu().double() - want_c).abs().max()) <= 1e-4
+    c, prev = C0.to(dev), None
+    for _ in range(4):
+        dist, idx = km.assign(X.to(dev), c)
+        total = float(dist.sum())
+        assert prev is None or total <= prev * (1 + 1e-6)
+        prev = total
+        c, _ = km.update(X.to(dev), idx, c)
+    fc, fi, fd = km.fit(X.to(dev), C0.to(dev), iters=3)
+    assert fc.shape == (k, d) and fi.shape == (n,) and fd.shape == (n,)
+    # many points, few clusters: the update gathers per-CTA partial sums in shared memory
+    n2 = 70001
+    X2 = torch.randn(n2, d, generator=g)
+    idx2 = torch.randint(0, k, (n2,), generator=g)
+    newc2, counts2 = km.update(X2.to(dev), idx2.to(dev), C0.to(dev))
+    want_c2, want_n2 = R.kmeans_update(X2, idx2, C0)
+    assert torch.equal(counts2.cpu().double(), want_n2)
+    assert float((newc2.cpu().double() - want_c2).abs().max()) <= 1e-4
+    assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
+
+
 # ----------------------------------------------------------------------------- l2 distance
 @pytest.mark.parametrize("shape", [(1, 200, 40, 300), (2, 130, 64, 257), (1, 1100, 96, 1300), (1, 64, 200, 520)])
 def test_min_and_topk_l2_distance(dev, lib, shape):

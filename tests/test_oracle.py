@@ -183,3 +183,15 @@ def test_l2_distance_restatements_agree():
         ctv, cti = CO.topk_bmm(A, B, 4, dim, distance="l2")
         assert torch.equal(tv, ctv)
         R.check_topk(ctv, cti, A, B, 4, dim, distance="l2")
+
+
+def test_kmeans_oracle_step():
+    """The k-means restatement on a case small enough to do by hand."""
+    X = torch.tensor([[0., 0.], [0., 2.], [10., 10.], [10., 12.], [5., 5.]])
+    C = torch.tensor([[0., 1.], [10., 11.], [100., 100.]])
+    v, i = R.kmeans_assign(X, C)
+    assert i.tolist() == [0, 0, 1, 1, 0]  # (5,5): 41 to the first centroid, 61 to the second
+    assert v.tolist() == [1.0, 1.0, 1.0, 1.0, 41.0]
+    newc, counts = R.kmeans_update(X, i, C)
+    assert counts.tolist() == [3.0, 2.0, 0.0]
+    assert torch.allclose(newc, torch.tensor([[5 / 3, 7 / 3], [10., 11.], [100., 100.]], dtype=torch.float64))
