@@ -948,3 +948,206 @@ extern "C" int fbmm_min_bmm_f32_noalloc(void* stream_, const float* A, int a_lay
   FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// 16-bit operands (fp16 / bf16): multiplied as they are by tcgen05.mma.kind::f16, fp32
+// accumulation. Both operands k-contiguous: A stored [l][m][k], B stored [l][n][k].
+// ---------------------------------------------------------------------------------------
+namespace {
+
+int check_dtype_x16(int dtype) {
+  if (dtype != FBMM_F16 && dtype != FBMM_BF16)
+    return fail(FBMM_ERR_INVALID, "dtype must be FBMM_F16 (1) or FBMM_BF16 (2), got %d", dtype);
+  return FBMM_OK;
+}
+
+int check_operand_x16(const char* name, const Operand& op, int k, int l) {
+  if (op.ptr == nullptr) return fail(FBMM_ERR_INVALID, "%s is null", name);
+  if (op.ld < k) return fail(FBMM_ERR_INVALID, "%s pitch %lld smaller than k = %d", name, op.ld, k);
+  if ((reinterpret_cast<uintptr_t>(op.ptr) & 15u) != 0) return fail(FBMM_ERR_ALIGN, "%s is not 16-byte aligned", name);
+  if ((op.ld & 7) != 0) return fail(FBMM_ERR_ALIGN, "%s pitch %lld is not a multiple of 8 elements", name, op.ld);
+  if (l > 1 && ((op.stride & 7) != 0 || op.stride < 0))
+    return fail(FBMM_ERR_ALIGN, "%s batch stride %lld is not a non-negative multiple of 8 elements", name, op.stride);
+  return FBMM_OK;
+}
+
+// K-major tensor map over 2-byte elements: dims (k, rows, l), box (64, box_rows, 1), i.e.
+// 128 bytes per row, 128-byte swizzle. Pitches in `op` count elements.
+int make_tensor_map_x16(CUtensorMap* map, const Operand& op, int k, int l, int box_rows, int dtype) {
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(op.rows), static_cast<cuuint64_t>(l)};
+  cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint64_t pitch_bytes = static_cast<cuuint64_t>(op.ld) * 2u;
+  cuuint64_t strides[2] = {pitch_bytes, l > 1 ? static_cast<cuuint64_t>(op.stride) * 2u : pitch_bytes * dims[1]};
+  if (strides[1] == 0) strides[1] = pitch_bytes;
+  cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = g_encode(map, dtype == FBMM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                              3, const_cast<float*>(op.ptr), dims, strides, box, elem_strides,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FBMM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return FBMM_OK;
+}
+
+template <int EPI, int E, bool AR, int DT>
+int launch_one_x16(const cudaLaunchConfig_t& cfg, const CUtensorMap& ta, const CUtensorMap& tb, const GemmShape& shape,
+                   const EpiArgs& epi) {
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, AR, true, false, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kSmemLimit)));
+  FBMM_CUDA(cudaLaunchKernelEx(&cfg, fbmm_gemm_kernel<EPI, E, AR, true, false, DT>, ta, tb, ta, tb, shape, epi));
+  return FBMM_OK;
+}
+
+// The fused kernel on 16-bit operands. `p` holds the operands with pitches in elements.
+template <int EPI, int E>
+int launch_gemm_x16(cudaStream_t stream, const DeviceState& st, const RowProblem& p, GemmShape shape, const EpiArgs& epi,
+                    int dtype) {
+  CUtensorMap ta, tb;
+  int rc;
+  if ((rc = make_tensor_map_x16(&ta, p.a, p.K, p.L, kTileM, dtype)) != FBMM_OK) return rc;
+  if ((rc = make_tensor_map_x16(&tb, p.b, p.K, p.L, kTileN, dtype)) != FBMM_OK) return rc;
+  const long long active = shape.num_units < st.sms ? shape.num_units : st.sms;
+  const int kblocks = (p.K + 2 * kKBlock - 1) / (2 * kKBlock);  // 64 elements per k-block
+  const bool a_resident = kblocks <= kMaxResidentKBlocks;
+  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, false);
+  if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(active), 1, 1);
+  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.dynamicSmemBytes = plan.total;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (dtype == FBMM_F16)
+    return a_resident ? launch_one_x16<EPI, E, true, 1>(cfg, ta, tb, shape, epi) : launch_one_x16<EPI, E, false, 1>(cfg, ta, tb, shape, epi);
+  return a_resident ? launch_one_x16<EPI, E, true, 2>(cfg, ta, tb, shape, epi) : launch_one_x16<EPI, E, false, 2>(cfg, ta, tb, shape, epi);
+}
+
+// Row-form problem of two k-contiguous 16-bit operands, checked.
+int make_row_problem_x16(RowProblem* p, const void* A, long long lda, long long stride_a, const void* B, long long ldb,
+                         long long stride_b, int l, int m, int n, int k, int dim) {
+  int rc;
+  if ((rc = make_row_problem(p, static_cast<const float*>(A), 'n', lda, stride_a, static_cast<const float*>(B), 't', ldb,
+                             stride_b, l, m, n, k, dim)) != FBMM_OK)
+    return rc;
+  if ((rc = check_operand_x16("A", dim == 2 ? p->a : p->b, k, l)) != FBMM_OK) return rc;
+  return check_operand_x16("B", dim == 2 ? p->b : p->a, k, l);
+}
+
+// shape with 128-row blocks whatever the pair setting of the fp32 kernels
+GemmShape base_shape_x16(const RowProblem& p) {
+  GemmShape s = base_shape(p);
+  s.m_blocks = (p.M + kTileM - 1) / kTileM;
+  return s;
+}
+
+}  // namespace
+
+extern "C" int fbmm_min_bmm_x16(void* stream_, const void* A, long long lda, long long stride_a, const void* B,
+                                long long ldb, long long stride_b, int dtype, float* values, long long* indices, int l,
+                                int m, int n, int k, int dim, void* workspace, size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if ((rc = check_dtype_x16(dtype)) != FBMM_OK) return rc;
+  if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
+  RowProblem p;
+  if ((rc = make_row_problem_x16(&p, A, lda, stride_a, B, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
+  const size_t need = fbmm_min_bmm_workspace_bytes(l, m, n, k, dim, FBMM_DIST_INNER);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(FBMM_ERR_WORKSPACE, "min_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 16-byte aligned");
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape_x16(p);
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  const long long rows = static_cast<long long>(l) * p.M;
+  unsigned long long* keys = static_cast<unsigned long long*>(workspace);
+  FBMM_CUDA(cudaMemsetAsync(keys, 0xff, static_cast<size_t>(rows) * 8, stream));
+  EpiArgs e{};
+  e.keys = keys;
+  if ((rc = launch_gemm_x16<kEpiMin, 1>(stream, *st, p, s, e, dtype)) != FBMM_OK) return rc;
+  const int threads = 256;
+  fbmm_min_finalize_kernel<<<static_cast<unsigned>((rows + threads - 1) / threads), threads, 0, stream>>>(keys, values,
+                                                                                                        indices, rows);
+  FBMM_CUDA(cudaGetLastError());
+  return FBMM_OK;
+}
+
+extern "C" int fbmm_topk_bmm_x16(void* stream_, const void* A, long long lda, long long stride_a, const void* B,
+                                 long long ldb, long long stride_b, int dtype, float* values, long long* indices, int l,
+                                 int m, int n, int k, int topk, int dim, long long index_offset, void* workspace,
+                                 size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if ((rc = check_dtype_x16(dtype)) != FBMM_OK) return rc;
+  if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
+  if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
+  RowProblem p;
+  if ((rc = make_row_problem_x16(&p, A, lda, stride_a, B, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
+  if (static_cast<long long>(p.N) + index_offset > 0x7ffffffell || index_offset < 0)
+    return fail(FBMM_ERR_INVALID, "column indices (offset %lld + %d columns) must stay below 2^31 - 1", index_offset, p.N);
+  const size_t need = fbmm_topk_bmm_workspace_bytes(l, m, n, k, topk, dim, FBMM_DIST_INNER);
+  if (workspace == nullptr || workspace_bytes < need)
+    return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape_x16(p);
+  // the same chunking as the workspace query assumed (which follows the fp32 kernels)
+  topk_plan(l, p.M, p.N, st->sms, &s.n_chunks, &s.tiles_per_chunk);
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  const long long rows = static_cast<long long>(l) * p.M;
+  EpiArgs e{};
+  e.k = topk;
+  e.index_offset = index_offset;
+  size_t own = 0;
+  if (s.n_chunks > 1) {
+    const size_t entries = static_cast<size_t>(s.n_chunks) * rows * topk;
+    e.topk_values = static_cast<float*>(workspace);
+    e.topk_indices = reinterpret_cast<long long*>(static_cast<char*>(workspace) + align_up(entries * sizeof(float), 256));
+    e.topk_chunk_rows = rows;
+    own = align_up(align_up(entries * sizeof(float), 256) + entries * sizeof(long long), 256);
+  } else {
+    e.topk_values = values;
+    e.topk_indices = indices;
+    e.topk_chunk_rows = 0;
+  }
+  e.topk_scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + own);
+  if (topk <= 64) rc = launch_gemm_x16<kEpiTopk, 2>(stream, *st, p, s, e, dtype);
+  else rc = launch_gemm_x16<kEpiTopk, 4>(stream, *st, p, s, e, dtype);
+  if (rc != FBMM_OK) return rc;
+  if (s.n_chunks > 1)
+    return fbmm_topk_merge_f32(stream_, e.topk_values, e.topk_indices, s.n_chunks, rows, topk, values, indices);
+  return FBMM_OK;
+}
+
+extern "C" int fbmm_bmm_x16(void* stream_, const void* A, long long lda, long long stride_a, const void* B,
+                            long long ldb, long long stride_b, int dtype, void* C, long long ldc, long long stride_c,
+                            int l, int m, int n, int k) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if ((rc = check_dtype_x16(dtype)) != FBMM_OK) return rc;
+  if (C == nullptr) return fail(FBMM_ERR_INVALID, "C is null");
+  if (ldc < n) return fail(FBMM_ERR_INVALID, "ldc %lld smaller than n = %d", ldc, n);
+  if ((reinterpret_cast<uintptr_t>(C) & 1u) != 0) return fail(FBMM_ERR_ALIGN, "C is not 2-byte aligned");
+  RowProblem p;
+  if ((rc = make_row_problem_x16(&p, A, lda, stride_a, B, ldb, stride_b, l, m, n, k, 2)) != FBMM_OK) return rc;
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape_x16(p);
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  EpiArgs e{};
+  e.C = static_cast<float*>(C);  // elements are 2 bytes wide; ldc and stride_c count elements
+  e.ldc = ldc;
+  e.stride_c = stride_c;
+  return launch_gemm_x16<kEpiStore, 1>(stream, *st, p, s, e, dtype);
+}

@@ -23,6 +23,8 @@
 // units i, i + gridDim.x, ... All four roles walk the same unit list.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cfloat>
 #include "sm100_primitives.cuh"
 
@@ -146,6 +148,19 @@ __device__ __forceinline__ float split_lo(float x) {
 // and a compare-exchange then costs four times as much.
 __device__ __forceinline__ bool topk_before(float va, int ia, float vb, int ib) {
   return (va > vb) | ((va == vb) & (ia < ib));
+}
+
+// Two fp32 values rounded to nearest into one 32-bit word of fp16 (bf16 == false) or bf16.
+__device__ __forceinline__ uint32_t pack_x16(float a, float b, bool bf16) {
+  if (bf16) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  const __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint16_t round_x16(float a, bool bf16) {
+  return static_cast<uint16_t>(pack_x16(a, 0.f, bf16) & 0xffffu);
 }
 
 // Within each group of four lanes, turns "lane q holds 32 consecutive columns of its own
@@ -576,7 +591,14 @@ __device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint
 // release both CTAs' stages. Results are identical to the single-CTA kernels; the whole
 // kernel is currently ~20 % slower than they are (the tensor pipe sits idle between pair
 // MMAs for a reason not yet found), so the library uses pairs only when asked to.
-template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT, bool PAIR>
+//
+// DT: element type of the operands. 0 = fp32 (everything above). 1 = fp16, 2 = bf16: the
+// operands are multiplied as they are by tcgen05.mma.kind::f16 (fp32 accumulation), one MMA
+// per k-step into the big accumulator only; a k-block is 64 elements (still 128 bytes per
+// row), there are no lo planes and nothing to split, so these variants are instantiated with
+// PRESPLIT = true and PAIR = false and load the hi planes only. Both operands must be
+// k-contiguous. The lo-plane slots of the shared-memory plan stay unused.
+template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT, bool PAIR, int DT = 0>
 __global__ void __launch_bounds__(kNumThreads, 1)
 fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_a_lo, const __grid_constant__ CUtensorMap tmap_b_lo,
@@ -585,7 +607,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr int kAccStages = 2;
   static_assert(2 * kAccStages * TILE_N <= kTmemCols, "TMEM budget");
 
-  const int kblocks = (shape.K + kKBlock - 1) / kKBlock;
+  constexpr bool kHalf = DT != 0;
+  static_assert(!kHalf || (PRESPLIT && !PAIR), "16-bit variants: PRESPLIT = true, PAIR = false");
+  constexpr int kKElems = kHalf ? 2 * kKBlock : kKBlock;  // elements of K per k-block (128 bytes)
+  const int kblocks = (shape.K + kKElems - 1) / kKElems;
   const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, PAIR);
   const uint32_t stages = plan.stages;
   constexpr uint32_t kBPlane = PAIR ? kPlaneBytes / 2u : kPlaneBytes;  // this CTA's part of a B tile plane
@@ -631,7 +656,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (PRESPLIT) {
+    if (PRESPLIT && !kHalf) {
       tma_prefetch_desc(&tmap_a_lo);
       tma_prefetch_desc(&tmap_b_lo);
     }
@@ -706,7 +731,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // this CTA's 128 rows of A, k-block kb
   auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int mb, int b) {
     if (!shape.a_mn) {
-      tma_issue(dst, map, bar, to_leader, kb * kKBlock, row_base(mb), b, a_policy);
+      tma_issue(dst, map, bar, to_leader, kb * kKElems, row_base(mb), b, a_policy);
     } else {
 #pragma unroll
       for (int c = 0; c < kTileM / 32; ++c)
@@ -717,7 +742,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   auto load_b = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int t, int b) {
     const int col = t * TILE_N + static_cast<int>(cta_rank) * kBCols;
     if (!shape.b_mn) {
-      tma_issue(dst, map, bar, to_leader, kb * kKBlock, col, b, kL2EvictLast);
+      tma_issue(dst, map, bar, to_leader, kb * kKElems, col, b, kL2EvictLast);
     } else {
 #pragma unroll
       for (int c = 0; c < kBCols / 32; ++c)
@@ -785,7 +810,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!ok) break;
             uint8_t* sb = ring + stage * plan.stage_bytes;
             // bytes this CTA brings into the stage
-            constexpr uint32_t kMyBytes = ((A_RES ? 0u : kPlaneBytes) + kBPlane) * (PRESPLIT ? 2u : 1u);
+            constexpr uint32_t kMyBytes = ((A_RES ? 0u : kPlaneBytes) + kBPlane) * ((PRESPLIT && !kHalf) ? 2u : 1u);
             // With pre-split planes nothing stands between the copies and the MMAs, so a
             // pair counts both CTAs' bytes on the even CTA's barrier, which that CTA arms.
             constexpr bool kToLeader = PAIR && PRESPLIT;
@@ -793,10 +818,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             else if (cta_rank == 0) mbar_arrive_expect_tx(&bars->full[stage], 2u * kMyBytes);
             if (!A_RES) {
               load_a(&tmap_a, sb + off_a_hi, &bars->full[stage], kToLeader, kb, mb, b);
-              if (PRESPLIT) load_a(&tmap_a_lo, sb + off_a_lo, &bars->full[stage], kToLeader, kb, mb, b);
+              if (PRESPLIT && !kHalf) load_a(&tmap_a_lo, sb + off_a_lo, &bars->full[stage], kToLeader, kb, mb, b);
             }
             load_b(&tmap_b, sb + off_b_hi, &bars->full[stage], kToLeader, kb, t, b);
-            if (PRESPLIT) load_b(&tmap_b_lo, sb + off_b_lo, &bars->full[stage], kToLeader, kb, t, b);
+            if (PRESPLIT && !kHalf) load_b(&tmap_b_lo, sb + off_b_lo, &bars->full[stage], kToLeader, kb, t, b);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
         }
@@ -862,7 +887,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t acc_small = acc_big + TILE_N;
           for (int kb = 0; kb < kblocks; ++kb) {
             if (A_RES && t == first) {
-              ok = wait_gate(&bars->a_split[kb], a_phase);
+              // 16-bit operands are used as they land; fp32 ones once their lo plane exists
+              ok = wait_gate(kHalf ? &bars->a_full[kb] : &bars->a_split[kb], a_phase);
               if (!ok) break;
             }
             FBMM_PROF_BEGIN();
@@ -881,7 +907,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t first_kb = kb == 0 ? 0u : 1u;
             const uint32_t a_hi0 = ((sa + off_a_hi) >> 4) | a_lbo_bits, a_lo0 = ((sa + off_a_lo) >> 4) | a_lbo_bits;
             const uint32_t b_hi0 = ((sb + off_b_hi) >> 4) | b_lbo_bits, b_lo0 = ((sb + off_b_lo) >> 4) | b_lbo_bits;
-            if (PAIR) {
+            if (kHalf) {
+              const uint32_t idesc_half = make_idesc_f16(kTileM, TILE_N, DT == 2);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks)  // big (+)= A * B, 16 elements of K per MMA
+                umma_f16(acc_big, pack(a_hi0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi),
+                         idesc_half, ks == 0 ? first_kb : 1u);
+              (void)a_lo0; (void)b_lo0; (void)acc_small; (void)idesc; (void)idesc_wide; (void)idesc_pair;
+            } else if (PAIR) {
 #pragma unroll
               for (int ks = 0; ks < kKBlock / 8; ++ks)  // small (+)= A_lo * B_hi
                 umma_tf32_pair(acc_small, pack(a_lo0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi),
@@ -920,8 +953,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ hi/lo splitters
-    if (PRESPLIT && !A_RES) {
-      // nothing to split: every lo plane arrives by TMA
+    if (kHalf || (PRESPLIT && !A_RES)) {
+      // nothing to split: every lo plane arrives by TMA, or (16-bit operands) there is none
     } else {
     const int st = static_cast<int>(threadIdx.x) - 64;
     uint32_t stage = 0, phase = 0, a_phase = 0;
@@ -1064,7 +1097,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint32_t rb[32], rs[32];
           FBMM_PROF_XBEGIN();
           tmem_ld_32x32b_x32(acc_big + c * 32, rb);
-          tmem_ld_32x32b_x32(acc_small + c * 32, rs);
+          if (!kHalf) tmem_ld_32x32b_x32(acc_small + c * 32, rs);
           tmem_ld_wait();
           FBMM_PROF_XEND(0);
           FBMM_PROF_XBEGIN();
@@ -1075,7 +1108,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           float v[32];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(rb[j]) + __uint_as_float(rs[j]);
+          for (int j = 0; j < 32; ++j) v[j] = kHalf ? __uint_as_float(rb[j]) : __uint_as_float(rb[j]) + __uint_as_float(rs[j]);
           const int col0 = col_tile + c * 32;
           if (l2) {
             // squared_l2 of the reference (kernels/bmm_helpers.cu:28-35) in GEMM form:
@@ -1132,12 +1165,32 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                   }
                 }
               }
+              if (kHalf) {
+                // C has the operands' type: eight columns are one 16-byte store, four lanes
+                // cover 64 contiguous bytes of a row
+                uint16_t* cb16 = reinterpret_cast<uint16_t*>(epi.C) + b * epi.stride_c +
+                                 static_cast<long long>(row_g) * epi.ldc + col0 + 8 * q;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  if (row_g + i < shape.M)
+                    __stcs(reinterpret_cast<uint4*>(cb16 + static_cast<long long>(i) * epi.ldc),
+                           make_uint4(pack_x16(v[8 * i], v[8 * i + 1], DT == 2), pack_x16(v[8 * i + 2], v[8 * i + 3], DT == 2),
+                                      pack_x16(v[8 * i + 4], v[8 * i + 5], DT == 2), pack_x16(v[8 * i + 6], v[8 * i + 7], DT == 2)));
+              } else {
 #pragma unroll
               for (int i = 0; i < 4; ++i)
                 if (row_g + i < shape.M)
                   st_global_v8_streaming(cbase + static_cast<long long>(i) * epi.ldc, v[8 * i], v[8 * i + 1],
                                          v[8 * i + 2], v[8 * i + 3], v[8 * i + 4], v[8 * i + 5], v[8 * i + 6],
                                          v[8 * i + 7]);
+              }
+            } else if (kHalf && row_ok && col0 < shape.N) {
+              // ragged right edge or unaligned rows of a 16-bit C: one row per thread, element-wise
+              uint16_t* crow16 = reinterpret_cast<uint16_t*>(epi.C) + b * epi.stride_c +
+                                 static_cast<long long>(row) * epi.ldc + col0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < shape.N) crow16[j] = round_x16(v[j], DT == 2);
             } else if (row_ok && col0 < shape.N) {
               // ragged right edge or storage that is not 32-byte friendly: one row per thread
               if (EPI == kEpiMask) {

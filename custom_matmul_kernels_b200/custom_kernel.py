@@ -66,6 +66,12 @@ SIGNATURES = {
     "fbmm_topk_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                           _c_int, _c_int, _c_ll, _c_ptr, _c_size]),
     "fbmm_topk_merge_f32": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr]),
+    "fbmm_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ll, _c_ll, _c_int,
+                              _c_int, _c_int, _c_int]),
+    "fbmm_min_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ptr, _c_int,
+                                  _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_size]),
+    "fbmm_topk_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ptr, _c_int,
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_size]),
     "fbmm_kmeans_update_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "fbmm_kmeans_update_f32": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr, _c_ll, _c_ptr,
                                         _c_ptr, _c_size]),
@@ -135,6 +141,31 @@ def operand(X: torch.Tensor):
     return buf, False, cp, r * cp
 
 
+FBMM_F16, FBMM_BF16 = 1, 2
+
+
+def dtype_code_x16(dtype: torch.dtype) -> int:
+    return FBMM_F16 if dtype == torch.float16 else FBMM_BF16
+
+
+def operand_x16(X: torch.Tensor):
+    """Describes a 16-bit [l, r, k] CUDA tensor to the *_x16 entry points, which take
+    k-contiguous storage only. Returns (tensor_to_keep_alive, pitch, batch_stride) in
+    elements. Anything else (k not contiguous, pitch or batch stride not a multiple of 8
+    elements, unaligned base) is copied into a row-major buffer with the pitch rounded up
+    to 8 elements."""
+    l, r, k = X.shape
+    sl, sr, sk = X.stride()
+    if (sk == 1 and X.data_ptr() % 16 == 0 and sr % 8 == 0 and sr >= k
+            and (l == 1 or (sl % 8 == 0 and sl > 0))):
+        return X, sr, sl
+    kp = (k + 7) // 8 * 8
+    buf = torch.zeros((l, r, kp), dtype=X.dtype, device=X.device) if kp != k else torch.empty(
+        (l, r, k), dtype=X.dtype, device=X.device)
+    buf[:, :, :k] = X
+    return buf, kp, r * kp
+
+
 def layout_letter(transposed: bool, is_b: bool) -> int:
     """'n'/'t' as the reference kernel suffixes use them: a row-major [m,k] A is 'n', a
     row-major [k,n] B is 'n' (bmm.py:56-66)."""
@@ -154,7 +185,7 @@ class CustomKernel:
         return torch.cuda.current_stream(device).cuda_stream
 
     @staticmethod
-    def check_inputs(A: torch.Tensor, B: torch.Tensor):
+    def check_inputs(A: torch.Tensor, B: torch.Tensor, dtypes=(torch.float32,)):
         """Shared argument checks of the wrappers (bmm.py:75-90, minbmm.py:84-99)."""
         if A.dim() != B.dim():
             raise ValueError("A and B need the same number of dimensions")
@@ -170,8 +201,9 @@ class CustomKernel:
             raise ValueError(f"inner dimensions differ: A {tuple(A3.shape)} B {tuple(B3.shape)}")
         if A3.dtype != B3.dtype:
             raise TypeError("A and B need the same dtype")
-        if A3.dtype != torch.float32:
-            raise TypeError(f"only float32 is implemented (the reference kernels take float* only), got {A3.dtype}")
+        if A3.dtype not in dtypes:
+            raise TypeError(f"dtype {A3.dtype} is not implemented for this op (the reference kernels take float* "
+                            f"only); accepted: {', '.join(str(d) for d in dtypes)}")
         if A3.device.type != "cuda" or B3.device.type != "cuda":
             raise ValueError("A and B must be CUDA tensors")
         if A3.device != B3.device:

@@ -96,7 +96,9 @@ def test_wrappers_reject_bad_inputs_on_cpu():
         with pytest.raises(ValueError):
             op(A, torch.zeros(2, 7, 4))
         with pytest.raises(TypeError):
-            op(A.half(), B.half())
+            op(A.double(), B.double())
+        with pytest.raises(TypeError):
+            op(A.half(), B)  # dtypes differ
         with pytest.raises(ValueError):
             op(A[0], B)
     with pytest.raises(NotImplementedError):
@@ -106,6 +108,18 @@ def test_wrappers_reject_bad_inputs_on_cpu():
         TopkBMMCUDA(distance="cosine")
     assert BMMCUDA().get_mode(A, B.transpose(1, 2).contiguous().transpose(1, 2)) == "nt"
     assert MBMMCUDA(share_mask=True).share_mask is True
+
+
+def test_operand_x16_descriptor_logic():
+    """`operand_x16` passes k-contiguous, 8-element-aligned storage through and repacks the rest."""
+    from custom_matmul_kernels_b200.custom_kernel import operand_x16
+    X = torch.zeros(2, 5, 16, dtype=torch.float16)
+    keep, ld, st = operand_x16(X)
+    assert keep is X and (ld, st) == (16, 80)
+    keep, ld, st = operand_x16(torch.zeros(2, 16, 5, dtype=torch.float16).transpose(1, 2))  # k not contiguous
+    assert keep.shape == (2, 5, 16) and keep.is_contiguous() and (ld, st) == (16, 80)
+    keep, ld, st = operand_x16(torch.ones(1, 3, 12, dtype=torch.bfloat16))  # pitch 12 is not a multiple of 8
+    assert keep.shape == (1, 3, 16) and (ld, st) == (16, 48) and float(keep[0, 0, 11]) == 1 and float(keep[0, 0, 12]) == 0
 
 
 def test_operand_descriptor_logic():

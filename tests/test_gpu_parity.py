@@ -406,6 +406,66 @@ def test_topk_and_min_on_a_repacked_column_operand(ops, dev, lib):
     assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
 
 
+# ----------------------------------------------------------------------------- 16-bit operands
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 300, 72, 700), (2, 129, 64, 257), (1, 1100, 200, 1300), (1, 64, 520, 3000)])
+def test_min_and_topk_on_16_bit_operands(ops, dev, lib, dtype, shape):
+    """fp16 / bf16 operands go to tcgen05.mma.kind::f16 as they are (fp32 accumulation). The
+    oracle multiplies the same 16-bit values in fp64, so only the accumulation differs:
+    the fp32 tolerance holds. K = 72 and 200 are not multiples of the 64-element k-block,
+    K = 520 streams A (more than four k-blocks); both dims, B given [k][n] (repacked by the
+    wrapper) and [n][k] (taken as it is)."""
+    l, m, k, n = shape
+    g = torch.Generator().manual_seed(sum(shape) + (1 if dtype == torch.float16 else 2))
+    A = torch.randn(l, m, k, generator=g).to(dtype)
+    B = torch.randn(l, k, n, generator=g).to(dtype)
+    Bt = B.to(dev).transpose(1, 2).contiguous().transpose(1, 2)
+    Af, Bf = A.float(), B.float()
+    for dim in (1, 2):
+        v, i = ops["min"](A.to(dev), B.to(dev), dim=dim)
+        assert v.dtype == torch.float32 and i.dtype == torch.int64
+        R.check_min(v, i, Af, Bf, dim)
+        v2, i2 = ops["min"](A.to(dev), Bt, dim=dim)
+        assert torch.equal(v, v2) and torch.equal(i, i2)
+        for kk in (10, 64):
+            tv, ti = ops["topk"](A.to(dev), B.to(dev), k=kk, dim=dim)
+            R.check_topk(tv, ti, Af, Bf, kk, dim)
+    device_ok(lib)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_bmm_on_16_bit_operands(ops, dev, lib, dtype):
+    """C comes back in the operands' type: the fp64 product of the same 16-bit values,
+    rounded once, may differ from it by the fp32 accumulation error plus half a unit in the
+    last place of the 16-bit type (2^-11 relative for fp16, 2^-8 for bf16)."""
+    half_ulp = 2.0 ** -11 if dtype == torch.float16 else 2.0 ** -8
+    g = torch.Generator().manual_seed(17)
+    for (l, m, k, n) in [(2, 300, 72, 264), (1, 129, 520, 257), (3, 1024, 128, 1024)]:
+        A = torch.randn(l, m, k, generator=g).to(dtype)
+        B = torch.randn(l, k, n, generator=g).to(dtype)
+        want = torch.bmm(A.double(), B.double())
+        for Bd in (B.to(dev), B.to(dev).transpose(1, 2).contiguous().transpose(1, 2)):
+            C = ops["bmm"](A.to(dev), Bd)
+            assert C.dtype == dtype and C.shape == (l, m, n)
+            err = (C.cpu().double() - want).abs()
+            assert bool((err <= 1e-4 + (1e-5 + half_ulp * 1.01) * want.abs()).all()), float(err.max())
+    device_ok(lib)
+
+
+def test_16_bit_exact_small_integers(ops, dev, lib):
+    """Small-integer operands are exact in fp16 and bf16 and so is every partial sum: the
+    16-bit kernels must return the fp32 kernels' values and indices bit for bit."""
+    A, B = R.exact_inputs(1, 260, 96, 1500, seed=91, lo=-4, hi=4)
+    v32, i32 = ops["min"](A.to(dev), B.to(dev), dim=2)
+    t32v, t32i = ops["topk"](A.to(dev), B.to(dev), k=32, dim=2)
+    for dtype in (torch.float16, torch.bfloat16):
+        v, i = ops["min"](A.to(dev).to(dtype), B.to(dev).to(dtype), dim=2)
+        assert torch.equal(v, v32) and torch.equal(i, i32)
+        tv, ti = ops["topk"](A.to(dev).to(dtype), B.to(dev).to(dtype), k=32, dim=2)
+        assert torch.equal(tv, t32v) and torch.equal(ti, t32i)
+    device_ok(lib)
+
+
 # ----------------------------------------------------------------------------- k-means consumer
 def test_kmeans_step_and_fit(dev, lib):
     """assign = min_bmm with the l2 distance, update = fbmm_kmeans_update_f32. One step is
