@@ -1008,7 +1008,7 @@ int launch_gemm_x16(cudaStream_t stream, const DeviceState& st, const RowProblem
   const long long active = shape.num_units < st.sms ? shape.num_units : st.sms;
   const int kblocks = (p.K + 2 * kKBlock - 1) / (2 * kKBlock);  // 64 elements per k-block
   const bool a_resident = kblocks <= kMaxResidentKBlocks;
-  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, false);
+  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, false, 1u);
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(active), 1, 1);

@@ -537,11 +537,13 @@ constexpr uint32_t kSmemLimit = 232448;  // 227 KB per CTA on sm_100
 struct SmemPlan {
   uint32_t a_bytes, stage_bytes, stages, epi_bytes, total;
 };
-__host__ __device__ inline SmemPlan make_smem_plan(bool a_resident, int kblocks, bool topk, bool pair) {
+// `planes`: 2 for fp32 operands (hi and lo), 1 for 16-bit ones.
+__host__ __device__ inline SmemPlan make_smem_plan(bool a_resident, int kblocks, bool topk, bool pair,
+                                                   uint32_t planes = 2u) {
   SmemPlan p;
   const uint32_t b_plane = pair ? kPlaneBytes / 2u : kPlaneBytes;  // a CTA of a pair holds half of each B tile
-  p.a_bytes = a_resident ? static_cast<uint32_t>(kblocks) * 2u * kPlaneBytes : 0u;
-  p.stage_bytes = (a_resident ? 0u : 2u * kPlaneBytes) + 2u * b_plane;
+  p.a_bytes = a_resident ? static_cast<uint32_t>(kblocks) * planes * kPlaneBytes : 0u;
+  p.stage_bytes = (a_resident ? 0u : planes * kPlaneBytes) + planes * b_plane;
   p.epi_bytes = topk ? kTopkStageBytes : 0u;
   const uint32_t fixed = p.a_bytes + p.epi_bytes + kBarrierBytes + 1024u /* alignment slack */;
   uint32_t st = (kSmemLimit - fixed) / p.stage_bytes;
@@ -611,13 +613,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   static_assert(!kHalf || (PRESPLIT && !PAIR), "16-bit variants: PRESPLIT = true, PAIR = false");
   constexpr int kKElems = kHalf ? 2 * kKBlock : kKBlock;  // elements of K per k-block (128 bytes)
   const int kblocks = (shape.K + kKElems - 1) / kKElems;
-  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, PAIR);
+  constexpr uint32_t kPlanes = kHalf ? 1u : 2u;  // planes per operand tile in shared memory
+  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, PAIR, kPlanes);
   const uint32_t stages = plan.stages;
   constexpr uint32_t kBPlane = PAIR ? kPlaneBytes / 2u : kPlaneBytes;  // this CTA's part of a B tile plane
   constexpr int kBCols = PAIR ? TILE_N / 2 : TILE_N;                  // ... in columns
   // offsets inside a ring stage
   const uint32_t off_a_hi = 0, off_a_lo = kPlaneBytes;
-  const uint32_t off_b_hi = A_RES ? 0u : 2u * kPlaneBytes;
+  const uint32_t off_b_hi = A_RES ? 0u : kPlanes * kPlaneBytes;
   const uint32_t off_b_lo = off_b_hi + kBPlane;
 
   extern __shared__ uint8_t smem_raw[];
@@ -802,7 +805,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               ok = mbar_wait(&bars->a_empty[kb], a_phase ^ 1u, abort_flag);
               if (!ok) break;
               mbar_arrive_expect_tx(&bars->a_full[kb], kPlaneBytes);
-              load_a(&tmap_a, a_region + kb * 2 * kPlaneBytes + off_a_hi, &bars->a_full[kb], false, kb, mb, b);
+              load_a(&tmap_a, a_region + kb * kPlanes * kPlaneBytes + off_a_hi, &bars->a_full[kb], false, kb, mb, b);
             }
             FBMM_PROF_BEGIN();
             ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag);
@@ -899,7 +902,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // proxy, or through writers that ran fence.proxy.async before arriving)
             FBMM_PROF_BEGIN();
             const uint32_t sb = smem_u32(ring + stage * plan.stage_bytes);
-            const uint32_t sa = A_RES ? smem_u32(a_region + kb * 2 * kPlaneBytes) : sb;
+            const uint32_t sa = A_RES ? smem_u32(a_region + kb * kPlanes * kPlaneBytes) : sb;
             // Issue order: all four k-steps of one operand-plane combination before the
             // next combination. Consecutive MMAs then walk the same 128-byte shared-memory
             // rows, and the tensor core runs at its full rate (measured on pairs: 64 cycles
