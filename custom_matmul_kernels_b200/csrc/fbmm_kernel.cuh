@@ -1087,6 +1087,28 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
           continue;
         }
+        // Mask bytes of a 32-column chunk for this lane after the lane-quad transpose (lane q
+        // of a quad: columns [8q, 8q + 8) of the quad's four rows). They are fetched one
+        // chunk ahead -- the first chunk's before the wait for the accumulator -- because
+        // with one epilogue warp per scheduler a trip to L2 or HBM is otherwise waited out
+        // in full on every chunk.
+        unsigned char tmv_n[4] = {0, 0, 0, 0};
+        uint2 e8_n[4] = {};
+        auto mask_line_ok = [&](int col0) -> bool {
+          return EPI == kEpiMask && c_lines_ok && em_lines_ok && col0 + 32 <= shape.N;
+        };
+        auto mask_fetch = [&](int col0) {
+          const int q = static_cast<int>(lane & 3u);
+          const int row_g = row_base(mb) + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = min(row_g + i, shape.M - 1);
+            tmv_n[i] = epi.thread_mask[b * epi.tm_stride + static_cast<long long>(r >> 3) * epi.tm_cols + (col0 >> 3) + q];
+            e8_n[i] = *reinterpret_cast<const uint2*>(epi.element_mask + b * epi.em_stride +
+                                                      static_cast<long long>(r) * shape.N + col0 + 8 * q);
+          }
+        };
+        if (mask_line_ok(col_tile)) mask_fetch(col_tile);
         FBMM_PROF_BEGIN();
         ok = mbar_wait(&bars->acc_full[acc_stage], acc_phase, abort_flag);
         FBMM_PROF_END(0);
@@ -1098,6 +1120,13 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll 1
         for (int c = 0; c < TILE_N / 32; ++c) {
           uint32_t rb[32], rs[32];
+          unsigned char tmv[4];
+          uint2 e8[4];
+          if (EPI == kEpiMask) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { tmv[i] = tmv_n[i]; e8[i] = e8_n[i]; }
+            if (c + 1 < TILE_N / 32 && mask_line_ok(col_tile + (c + 1) * 32)) mask_fetch(col_tile + (c + 1) * 32);
+          }
           FBMM_PROF_XBEGIN();
           tmem_ld_32x32b_x32(acc_big + c * 32, rb);
           if (!kHalf) tmem_ld_32x32b_x32(acc_small + c * 32, rs);
@@ -1147,17 +1176,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               float* cbase = epi.C + b * epi.stride_c + static_cast<long long>(row_g) * epi.ldc + col0 + 8 * q;
               if (EPI == kEpiMask) {
                 // kernels/mbmm.cu:360-363 (8x8 tile skip) and :111-133 (element multiply);
-                // all mask bytes are fetched before the first store so the loads overlap
-                unsigned char tmv[4];
-                uint2 e8[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int r = min(row_g + i, shape.M - 1);
-                  tmv[i] = epi.thread_mask[b * epi.tm_stride + static_cast<long long>(r >> 3) * epi.tm_cols +
-                                           (col0 >> 3) + q];
-                  e8[i] = *reinterpret_cast<const uint2*>(epi.element_mask + b * epi.em_stride +
-                                                          static_cast<long long>(r) * shape.N + col0 + 8 * q);
-                }
+                // the mask bytes (tmv, e8) were fetched one chunk ahead
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
 #pragma unroll
