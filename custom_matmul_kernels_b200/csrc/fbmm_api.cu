@@ -407,7 +407,7 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
   const bool ps = kHasPresplit && presplit;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(active) * (pairs ? 2u : 1u), 1, 1);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.blockDim = dim3(block_threads(EPI), 1, 1);
   cfg.dynamicSmemBytes = plan.total;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1012,7 +1012,7 @@ int launch_gemm_x16(cudaStream_t stream, const DeviceState& st, const RowProblem
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(active), 1, 1);
-  cfg.blockDim = dim3(kNumThreads, 1, 1);
+  cfg.blockDim = dim3(block_threads(EPI), 1, 1);
   cfg.dynamicSmemBytes = plan.total;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];

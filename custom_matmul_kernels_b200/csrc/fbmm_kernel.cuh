@@ -32,13 +32,21 @@ namespace fbmm {
 
 constexpr int kTileM = 128;
 constexpr int kKBlock = 32;  // fp32 elements per k-block: one 128-byte swizzle row
-constexpr int kNumThreads = 320;
 constexpr int kSplitThreads = 128;
-constexpr int kEpiThreads = 128;
 constexpr int kTmemCols = 512;
 constexpr long long kPaceWaitCycles = 4000000;  // longest a CTA holds back for the others (~2 ms)
 
 enum EpilogueKind { kEpiStore = 0, kEpiMask = 1, kEpiMin = 2, kEpiTopk = 3 };
+
+// Epilogue warps. A warp may read only the 32 TMEM lanes (rows) 32 * (warp % 4) onwards, so
+// four warps cover a tile. The mask epilogue runs two warps per row quarter, each on half of
+// the tile's columns: one warp per scheduler cannot hide the latency of its own chain (TMEM
+// load, shuffles, mask bytes from HBM, stores), which was what held mbmm back (c3 216 ->
+// 199 us). The plain store epilogue is not what limits bmm and measured 6 % slower with
+// eight warps; the reducing epilogues keep one warp per row quarter because a row's state
+// has one owner.
+__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == kEpiMask ? 8 : 4; }
+__host__ __device__ constexpr int block_threads(int epi) { return 192 + 32 * epilogue_warps(epi); }
 
 // Device status word (bit 0: a bounded wait ran out).
 __device__ unsigned int g_fbmm_status[4];
@@ -601,7 +609,7 @@ __device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint
 // PRESPLIT = true and PAIR = false and load the hi planes only. Both operands must be
 // k-contiguous. The lo-plane slots of the shared-memory plan stay unused.
 template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT, bool PAIR, int DT = 0>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(block_threads(EPI), 1)
 fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_a_lo, const __grid_constant__ CUtensorMap tmap_b_lo,
                  const GemmShape shape, const EpiArgs epi) {
@@ -649,7 +657,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     for (int s = 0; s < kAccStages; ++s) {
       mbar_init(&bars->acc_full[s], 1);
-      mbar_init(&bars->acc_empty[s], kEpiThreads * kCtas);
+      mbar_init(&bars->acc_empty[s], 32 * epilogue_warps(EPI) * kCtas);
     }
     for (int s = 0; s < kMaxResidentKBlocks; ++s) {
       mbar_init(&bars->a_full[s], 1);
@@ -1003,6 +1011,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else {
     // ------------------------------------------------------------------ epilogue
     const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read
+    // 32-column chunks of a tile this warp handles
+    constexpr int kChunksPerWarp = (TILE_N / 32) / (epilogue_warps(EPI) / 4);
+    const int chunk_first = static_cast<int>((warp - 6u) >> 2) * kChunksPerWarp;
+    const int chunk_end = chunk_first + kChunksPerWarp;
     const int row_in_tile = static_cast<int>(quarter * 32u + lane);
     const uint32_t lane_base = (quarter * 32u) << 16;
     uint32_t acc_stage = 0, acc_phase = 0;
@@ -1067,12 +1079,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int i = 0; i < 4; ++i)
                 if (row_g + i < shape.M)
 #pragma unroll
-                  for (int c = 0; c < TILE_N; c += 32)
-                    st_global_v8_streaming(cbase + static_cast<long long>(i) * epi.ldc + c, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f,
-                                           0.f, 0.f);
+                  for (int c = 0; c < kChunksPerWarp * 32; c += 32)
+                    st_global_v8_streaming(cbase + static_cast<long long>(i) * epi.ldc + chunk_first * 32 + c, 0.f, 0.f,
+                                           0.f, 0.f, 0.f, 0.f, 0.f, 0.f);
             } else if (row_ok) {
               float* crow = epi.C + b * epi.stride_c + static_cast<long long>(row) * epi.ldc;
-              for (int c = col_tile; c < c_end; ++c) crow[c] = 0.f;
+              for (int c = col_tile + chunk_first * 32; c < min(c_end, col_tile + chunk_end * 32); ++c) crow[c] = 0.f;
             }
           }
         }
@@ -1108,7 +1120,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                                       static_cast<long long>(r) * shape.N + col0 + 8 * q);
           }
         };
-        if (mask_line_ok(col_tile)) mask_fetch(col_tile);
+        if (mask_line_ok(col_tile + chunk_first * 32)) mask_fetch(col_tile + chunk_first * 32);
         FBMM_PROF_BEGIN();
         ok = mbar_wait(&bars->acc_full[acc_stage], acc_phase, abort_flag);
         FBMM_PROF_END(0);
@@ -1118,14 +1130,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t acc_big = tmem_base + acc_stage * (2 * TILE_N) + lane_base;
         const uint32_t acc_small = acc_big + TILE_N;
 #pragma unroll 1
-        for (int c = 0; c < TILE_N / 32; ++c) {
+        for (int c = chunk_first; c < chunk_end; ++c) {
           uint32_t rb[32], rs[32];
           unsigned char tmv[4];
           uint2 e8[4];
           if (EPI == kEpiMask) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) { tmv[i] = tmv_n[i]; e8[i] = e8_n[i]; }
-            if (c + 1 < TILE_N / 32 && mask_line_ok(col_tile + (c + 1) * 32)) mask_fetch(col_tile + (c + 1) * 32);
+            if (c + 1 < chunk_end && mask_line_ok(col_tile + (c + 1) * 32)) mask_fetch(col_tile + (c + 1) * 32);
           }
           FBMM_PROF_XBEGIN();
           tmem_ld_32x32b_x32(acc_big + c * 32, rb);
@@ -1133,7 +1145,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           tmem_ld_wait();
           FBMM_PROF_XEND(0);
           FBMM_PROF_XBEGIN();
-          if (c == TILE_N / 32 - 1) {
+          if (c == chunk_end - 1) {
             // both accumulators of this stage are now in registers: hand the stage back
             tcgen05_fence_before_sync();
             arrive_leader(&bars->acc_empty[acc_stage]);
