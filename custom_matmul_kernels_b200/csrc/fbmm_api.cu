@@ -1151,3 +1151,36 @@ extern "C" int fbmm_bmm_x16(void* stream_, const void* A, long long lda, long lo
   e.stride_c = stride_c;
   return launch_gemm_x16<kEpiStore, 1>(stream, *st, p, s, e, dtype);
 }
+
+extern "C" int fbmm_mbmm_x16(void* stream_, const void* A, long long lda, long long stride_a, const void* B,
+                             long long ldb, long long stride_b, int dtype, void* C, long long ldc, long long stride_c,
+                             const unsigned char* block_mask, const unsigned char* thread_mask,
+                             const unsigned char* element_mask, int share_mask, int l, int m, int n, int k) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if ((rc = check_dtype_x16(dtype)) != FBMM_OK) return rc;
+  if (C == nullptr) return fail(FBMM_ERR_INVALID, "C is null");
+  if (ldc < n) return fail(FBMM_ERR_INVALID, "ldc %lld smaller than n = %d", ldc, n);
+  if ((reinterpret_cast<uintptr_t>(C) & 1u) != 0) return fail(FBMM_ERR_ALIGN, "C is not 2-byte aligned");
+  if (block_mask == nullptr || thread_mask == nullptr || element_mask == nullptr)
+    return fail(FBMM_ERR_INVALID, "a mask pointer is null");
+  RowProblem p;
+  if ((rc = make_row_problem_x16(&p, A, lda, stride_a, B, ldb, stride_b, l, m, n, k, 2)) != FBMM_OK) return rc;
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape_x16(p);
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
+  EpiArgs e{};
+  e.C = static_cast<float*>(C);  // elements are 2 bytes wide; ldc and stride_c count elements
+  e.ldc = ldc;
+  e.stride_c = stride_c;
+  e.block_mask = block_mask; e.thread_mask = thread_mask; e.element_mask = element_mask;
+  e.bm_cols = (n + 127) / 128;
+  e.tm_cols = (n + 7) / 8;
+  e.bm_stride = share_mask ? 0 : static_cast<long long>((m + 127) / 128) * e.bm_cols;
+  e.tm_stride = share_mask ? 0 : static_cast<long long>((m + 7) / 8) * e.tm_cols;
+  e.em_stride = share_mask ? 0 : static_cast<long long>(m) * n;
+  return launch_gemm_x16<kEpiMask, 1>(stream, *st, p, s, e, dtype);
+}

@@ -1070,7 +1070,13 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           // masked-out block: the product is defined as zero (mbmm.py:74 pre-zeroes C).
           if (EPI == kEpiMask) {
             const int c_end = min(shape.N, col_tile + TILE_N);
-            if (c_lines_ok && col_tile + TILE_N <= shape.N) {
+            if (kHalf) {
+              // 16-bit C: element-wise zeros over this warp's columns of the row
+              if (row_ok) {
+                uint16_t* crow16 = reinterpret_cast<uint16_t*>(epi.C) + b * epi.stride_c + static_cast<long long>(row) * epi.ldc;
+                for (int c = col_tile + chunk_first * 32; c < min(c_end, col_tile + chunk_end * 32); ++c) crow16[c] = 0;
+              }
+            } else if (c_lines_ok && col_tile + TILE_N <= shape.N) {
               // four lanes per row: every store instruction writes eight whole lines
               const int q = static_cast<int>(lane & 3u);
               const int row_g = row_base(mb) + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
@@ -1218,13 +1224,6 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                          v[8 * i + 2], v[8 * i + 3], v[8 * i + 4], v[8 * i + 5], v[8 * i + 6],
                                          v[8 * i + 7]);
               }
-            } else if (kHalf && row_ok && col0 < shape.N) {
-              // ragged right edge or unaligned rows of a 16-bit C: one row per thread, element-wise
-              uint16_t* crow16 = reinterpret_cast<uint16_t*>(epi.C) + b * epi.stride_c +
-                                 static_cast<long long>(row) * epi.ldc + col0;
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < shape.N) crow16[j] = round_x16(v[j], DT == 2);
             } else if (row_ok && col0 < shape.N) {
               // ragged right edge or storage that is not 32-byte friendly: one row per thread
               if (EPI == kEpiMask) {
@@ -1244,7 +1243,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
               }
               float* crow = epi.C + b * epi.stride_c + static_cast<long long>(row) * epi.ldc + col0;
-              if (col0 + 32 <= shape.N && (reinterpret_cast<uintptr_t>(crow) & 15) == 0) {
+              if (kHalf) {
+                // 16-bit C: element-wise
+                uint16_t* crow16 = reinterpret_cast<uint16_t*>(epi.C) + b * epi.stride_c +
+                                   static_cast<long long>(row) * epi.ldc + col0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < shape.N) crow16[j] = round_x16(v[j], DT == 2);
+              } else if (col0 + 32 <= shape.N && (reinterpret_cast<uintptr_t>(crow) & 15) == 0) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 4)
                   __stcs(reinterpret_cast<float4*>(crow + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));

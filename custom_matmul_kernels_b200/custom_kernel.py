@@ -68,6 +68,8 @@ SIGNATURES = {
     "fbmm_topk_merge_f32": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr]),
     "fbmm_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ll, _c_ll, _c_int,
                               _c_int, _c_int, _c_int]),
+    "fbmm_mbmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ll, _c_ll, _c_ptr,
+                               _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_min_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ptr, _c_int,
                                   _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_size]),
     "fbmm_topk_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ptr, _c_int,

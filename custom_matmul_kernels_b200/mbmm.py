@@ -5,7 +5,7 @@ import math
 
 import torch
 
-from .custom_kernel import CustomKernel, check, layout_letter, operand
+from .custom_kernel import CustomKernel, check, dtype_code_x16, layout_letter, operand, operand_x16
 
 
 def make_masks(mask: torch.Tensor):
@@ -62,12 +62,22 @@ class MBMMCUDA(CustomKernel):
         for name, shape in want.items():
             if tuple(got[name].shape) != shape:
                 raise ValueError(f"{name} has shape {tuple(got[name].shape)}, expected {shape}")
-        C = torch.empty((l, m, n), device=A.device, dtype=torch.float32)
+        C = torch.empty((l, m, n), device=A.device, dtype=A.dtype)
         if l == 0 or m == 0 or n == 0:
             return C
         if k == 0:
             return C.zero_()
         bm, tm, em = block_mask.contiguous(), thread_mask.contiguous(), element_mask.contiguous()
+        if A.dtype in (torch.float16, torch.bfloat16):
+            # fp16 / bf16 go to the tensor cores as they are; C comes back in their type
+            a_keep, lda, sa = operand_x16(A)
+            b_keep, ldb, sb = operand_x16(B.transpose(1, 2))
+            with torch.cuda.device(A.device):
+                check(self.lib.fbmm_mbmm_x16(
+                    self.stream_ptr(A.device), a_keep.data_ptr(), lda, sa, b_keep.data_ptr(), ldb, sb,
+                    dtype_code_x16(A.dtype), C.data_ptr(), n, m * n,
+                    bm.data_ptr(), tm.data_ptr(), em.data_ptr(), 1 if self.share_mask else 0, l, m, n, k))
+            return C
         a_keep, a_t, lda, sa = operand(A)
         b_keep, b_t, ldb, sb = operand(B)
         with torch.cuda.device(A.device):
@@ -90,7 +100,7 @@ class MBMMCUDA(CustomKernel):
         raise NotImplementedError
 
     def __call__(self, A, B, block_mask, thread_mask, element_mask, mode="nn"):
-        A3, B3, two_d = self.check_inputs(A, B)
+        A3, B3, two_d = self.check_inputs(A, B, (torch.float32, torch.float16, torch.bfloat16))
         A3 = A3.contiguous()
         B3 = B3.contiguous()
         if two_d and not self.share_mask:

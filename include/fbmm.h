@@ -167,8 +167,8 @@ int fbmm_topk_merge_f32(void* stream,
                         int groups, long long rows, int topk,
                         float* out_values, long long* out_indices);
 
-/* bmm, min_bmm and topk_bmm on fp16 / bf16 operands (dtype FBMM_F16 / FBMM_BF16), inner
- * product only; C of bmm has the operands' type (as the reference allocates it, bmm.py:106),
+/* bmm, mbmm, min_bmm and topk_bmm on fp16 / bf16 operands (dtype FBMM_F16 / FBMM_BF16), inner
+ * product only; C of bmm / mbmm has the operands' type (as the reference allocates it, bmm.py:106),
  * rounded to nearest from the fp32 accumulator, pitch ldc and batch stride in elements. The reference's wrappers admit torch.half (bmm.py:89, minbmm.py:98) but its kernels
  * take float* only (kernels/minbmm.cu:348-354), so half inputs never worked there; here the
  * operands go to the tensor cores as they are (tcgen05.mma.kind::f16, fp32 accumulation, no
@@ -180,6 +180,11 @@ int fbmm_topk_merge_f32(void* stream,
 int fbmm_bmm_x16(void* stream, const void* A, long long lda, long long stride_a,
                  const void* B, long long ldb, long long stride_b, int dtype,
                  void* C, long long ldc, long long stride_c, int l, int m, int n, int k);
+int fbmm_mbmm_x16(void* stream, const void* A, long long lda, long long stride_a,
+                  const void* B, long long ldb, long long stride_b, int dtype,
+                  void* C, long long ldc, long long stride_c,
+                  const unsigned char* block_mask, const unsigned char* thread_mask,
+                  const unsigned char* element_mask, int share_mask, int l, int m, int n, int k);
 int fbmm_min_bmm_x16(void* stream, const void* A, long long lda, long long stride_a,
                      const void* B, long long ldb, long long stride_b, int dtype,
                      float* values, long long* indices, int l, int m, int n, int k, int dim,

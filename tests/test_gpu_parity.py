@@ -452,6 +452,30 @@ def test_bmm_on_16_bit_operands(ops, dev, lib, dtype):
     device_ok(lib)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_mbmm_on_16_bit_operands(ops, dev, lib, dtype):
+    """Masked bmm with 16-bit operands: zeros exactly where the mask says so, the rounded
+    product elsewhere (shapes with ragged edges and with whole dead 128x128 blocks)."""
+    from custom_matmul_kernels_b200 import make_masks
+    half_ulp = 2.0 ** -11 if dtype == torch.float16 else 2.0 ** -8
+    g = torch.Generator().manual_seed(23)
+    for (l, m, k, n) in [(2, 300, 72, 264), (2, 512, 64, 640)]:
+        A = torch.randn(l, m, k, generator=g).to(dtype)
+        B = torch.randn(l, k, n, generator=g).to(dtype)
+        mask = torch.rand(l, m, n, generator=g) < 0.4
+        mask[0, :128, :256] = False          # dead blocks
+        mask[1] = torch.tril(torch.ones(m, n)).bool()
+        bm, tm, em = make_masks(mask.to(dev))
+        C = ops["mbmm"](A.to(dev), B.to(dev), bm, tm, em)
+        assert C.dtype == dtype
+        want = torch.bmm(A.double(), B.double()).masked_fill_(~mask, 0)
+        got = C.cpu().double()
+        assert bool((got[~mask] == 0).all())
+        err = (got - want).abs()
+        assert bool((err <= 1e-4 + (1e-5 + half_ulp * 1.01) * want.abs()).all()), float(err.max())
+    device_ok(lib)
+
+
 def test_16_bit_exact_small_integers(ops, dev, lib):
     """Small-integer operands are exact in fp16 and bf16 and so is every partial sum: the
     16-bit kernels must return the fp32 kernels' values and indices bit for bit."""
