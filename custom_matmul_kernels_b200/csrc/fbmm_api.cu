@@ -1045,19 +1045,41 @@ GemmShape base_shape_x16(const RowProblem& p) {
   return s;
 }
 
+// Squared norms of both 16-bit operands into `scratch` (norms_bytes); fills the epilogue arguments.
+int launch_norms_x16(cudaStream_t stream, const RowProblem& p, void* scratch, EpiArgs* e, int dtype) {
+  float* rn = static_cast<float*>(scratch);
+  float* cn = reinterpret_cast<float*>(static_cast<char*>(scratch) + align_up(static_cast<size_t>(p.L) * p.M * 4, 256));
+  const Operand* ops[2] = {&p.a, &p.b};
+  float* outs[2] = {rn, cn};
+  for (int i = 0; i < 2; ++i) {
+    const Operand& op = *ops[i];
+    const long long total = static_cast<long long>(p.L) * op.rows;
+    const int threads = 256;
+    const long long blocks = (total * 32 + threads - 1) / threads;
+    fbmm_sqnorm_x16_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(
+        reinterpret_cast<const uint16_t*>(op.ptr), outs[i], p.L, op.rows, p.K, op.ld, p.L > 1 ? op.stride : 0,
+        dtype == FBMM_BF16 ? 1 : 0);
+  }
+  FBMM_CUDA(cudaGetLastError());
+  e->row_norms = rn;
+  e->col_norms = cn;
+  return FBMM_OK;
+}
+
 }  // namespace
 
 extern "C" int fbmm_min_bmm_x16(void* stream_, const void* A, long long lda, long long stride_a, const void* B,
                                 long long ldb, long long stride_b, int dtype, float* values, long long* indices, int l,
-                                int m, int n, int k, int dim, void* workspace, size_t workspace_bytes) {
+                                int m, int n, int k, int dim, int distance, void* workspace, size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   int rc;
   if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
   if ((rc = check_dtype_x16(dtype)) != FBMM_OK) return rc;
+  if ((rc = check_distance(distance)) != FBMM_OK) return rc;
   if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
   RowProblem p;
   if ((rc = make_row_problem_x16(&p, A, lda, stride_a, B, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
-  const size_t need = fbmm_min_bmm_workspace_bytes(l, m, n, k, dim, FBMM_DIST_INNER);
+  const size_t need = fbmm_min_bmm_workspace_bytes(l, m, n, k, dim, distance);
   if (workspace == nullptr || workspace_bytes < need)
     return fail(FBMM_ERR_WORKSPACE, "min_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
   if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 16-byte aligned");
@@ -1071,6 +1093,10 @@ extern "C" int fbmm_min_bmm_x16(void* stream_, const void* A, long long lda, lon
   FBMM_CUDA(cudaMemsetAsync(keys, 0xff, static_cast<size_t>(rows) * 8, stream));
   EpiArgs e{};
   e.keys = keys;
+  if (distance == FBMM_DIST_L2 &&
+      (rc = launch_norms_x16(stream, p, static_cast<char*>(workspace) + align_up(static_cast<size_t>(rows) * 8, 256), &e,
+                             dtype)) != FBMM_OK)
+    return rc;
   if ((rc = launch_gemm_x16<kEpiMin, 1>(stream, *st, p, s, e, dtype)) != FBMM_OK) return rc;
   const int threads = 256;
   fbmm_min_finalize_kernel<<<static_cast<unsigned>((rows + threads - 1) / threads), threads, 0, stream>>>(keys, values,
@@ -1081,19 +1107,20 @@ extern "C" int fbmm_min_bmm_x16(void* stream_, const void* A, long long lda, lon
 
 extern "C" int fbmm_topk_bmm_x16(void* stream_, const void* A, long long lda, long long stride_a, const void* B,
                                  long long ldb, long long stride_b, int dtype, float* values, long long* indices, int l,
-                                 int m, int n, int k, int topk, int dim, long long index_offset, void* workspace,
-                                 size_t workspace_bytes) {
+                                 int m, int n, int k, int topk, int dim, int distance, long long index_offset,
+                                 void* workspace, size_t workspace_bytes) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   int rc;
   if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
   if ((rc = check_dtype_x16(dtype)) != FBMM_OK) return rc;
+  if ((rc = check_distance(distance)) != FBMM_OK) return rc;
   if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
   if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
   RowProblem p;
   if ((rc = make_row_problem_x16(&p, A, lda, stride_a, B, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
   if (static_cast<long long>(p.N) + index_offset > 0x7ffffffell || index_offset < 0)
     return fail(FBMM_ERR_INVALID, "column indices (offset %lld + %d columns) must stay below 2^31 - 1", index_offset, p.N);
-  const size_t need = fbmm_topk_bmm_workspace_bytes(l, m, n, k, topk, dim, FBMM_DIST_INNER);
+  const size_t need = fbmm_topk_bmm_workspace_bytes(l, m, n, k, topk, dim, distance);
   if (workspace == nullptr || workspace_bytes < need)
     return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
   if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
@@ -1118,6 +1145,10 @@ extern "C" int fbmm_topk_bmm_x16(void* stream_, const void* A, long long lda, lo
     e.topk_values = values;
     e.topk_indices = indices;
     e.topk_chunk_rows = 0;
+  }
+  if (distance == FBMM_DIST_L2) {
+    if ((rc = launch_norms_x16(stream, p, static_cast<char*>(workspace) + own, &e, dtype)) != FBMM_OK) return rc;
+    own += norms_bytes(p);
   }
   e.topk_scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + own);
   if (topk <= 64) rc = launch_gemm_x16<kEpiTopk, 2>(stream, *st, p, s, e, dtype);

@@ -1447,6 +1447,24 @@ __global__ void fbmm_sqnorm_kernel(const float* __restrict__ x, float* __restric
   }
 }
 
+// The same for k-contiguous fp16 (bf16 == 0) or bf16 rows, one warp per row, fp32 sums.
+__global__ void fbmm_sqnorm_x16_kernel(const uint16_t* __restrict__ x, float* __restrict__ out, int L, int rows, int K,
+                                       long long ld, long long stride, int bf16) {
+  const long long total = static_cast<long long>(L) * rows;
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (i >= total) return;  // whole warps leave together
+  const uint16_t* p = x + (i / rows) * stride + (i % rows) * ld;
+  float acc = 0.f;
+  for (int k = static_cast<int>(lane_id()); k < K; k += 32) {
+    const uint16_t raw = p[k];
+    const float a = bf16 ? __uint_as_float(static_cast<uint32_t>(raw) << 16) : __half2float(__ushort_as_half(raw));
+    acc = fmaf(a, a, acc);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane_id() == 0) out[i] = acc;
+}
+
 // keys -> (values, indices) for min_bmm
 __global__ void fbmm_min_finalize_kernel(const unsigned long long* __restrict__ keys, float* __restrict__ values,
                                          long long* __restrict__ indices, long long count) {

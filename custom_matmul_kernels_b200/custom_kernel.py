@@ -71,9 +71,9 @@ SIGNATURES = {
     "fbmm_mbmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ll, _c_ll, _c_ptr,
                                _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_min_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ptr, _c_int,
-                                  _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_size]),
+                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_size]),
     "fbmm_topk_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ptr, _c_int,
-                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_size]),
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ptr, _c_size]),
     "fbmm_kmeans_update_workspace_bytes": (_c_size, [_c_int, _c_int]),
     "fbmm_kmeans_update_f32": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ptr, _c_ll, _c_int, _c_int, _c_ptr, _c_ll, _c_ptr,
                                         _c_ptr, _c_size]),

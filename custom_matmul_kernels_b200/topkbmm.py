@@ -54,17 +54,16 @@ class TopkBMMCUDA(CustomKernel):
         indices = torch.empty((l, rows, k), device=A3.device, dtype=torch.int64)
         if A3.dtype in _X16:
             # fp16 / bf16 go to the tensor cores as they are; values come back in fp32
-            if self._distance_code != 0:
-                raise NotImplementedError("16-bit inputs: only distance='inner' is implemented")
             a_keep, lda, sa = operand_x16(A3)
             b_keep, ldb, sb = operand_x16(B3.transpose(1, 2))
             with torch.cuda.device(A3.device):
-                ws_bytes = (self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim, 0) + 255) // 256 * 256
+                ws_bytes = (self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim, self._distance_code)
+                            + 255) // 256 * 256
                 ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
                 check(self.lib.fbmm_topk_bmm_x16(
                     self.stream_ptr(A3.device), a_keep.data_ptr(), lda, sa, b_keep.data_ptr(), ldb, sb,
                     dtype_code_x16(A3.dtype), values.data_ptr(), indices.data_ptr(), l, m, n, d, k, dim,
-                    index_offset, ws.data_ptr(), ws_bytes))
+                    self._distance_code, index_offset, ws.data_ptr(), ws_bytes))
             return (values[0], indices[0]) if two_d else (values, indices)
         a_keep, a_t, lda, sa = operand(A3)
         b_keep, b_t, ldb, sb = operand(B3)

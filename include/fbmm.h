@@ -167,16 +167,15 @@ int fbmm_topk_merge_f32(void* stream,
                         int groups, long long rows, int topk,
                         float* out_values, long long* out_indices);
 
-/* bmm, mbmm, min_bmm and topk_bmm on fp16 / bf16 operands (dtype FBMM_F16 / FBMM_BF16), inner
- * product only; C of bmm / mbmm has the operands' type (as the reference allocates it, bmm.py:106),
+/* bmm, mbmm, min_bmm and topk_bmm on fp16 / bf16 operands (dtype FBMM_F16 / FBMM_BF16); C of
+ * bmm / mbmm has the operands' type (as the reference allocates it, bmm.py:106),
  * rounded to nearest from the fp32 accumulator, pitch ldc and batch stride in elements. The reference's wrappers admit torch.half (bmm.py:89, minbmm.py:98) but its kernels
  * take float* only (kernels/minbmm.cu:348-354), so half inputs never worked there; here the
  * operands go to the tensor cores as they are (tcgen05.mma.kind::f16, fp32 accumulation, no
  * three-way split). Both operands must be k-contiguous: A stored [l][m][k] with pitch lda,
  * B stored [l][n][k] with pitch ldb (pitches and batch strides in elements, multiples of 8;
- * bases 16-byte aligned). values fp32, indices int64; dim, ties, padding, topk,
- * index_offset and the workspace (same queries, distance FBMM_DIST_INNER) as for the f32
- * entry points. */
+ * bases 16-byte aligned). values fp32, indices int64; dim, distance, ties, padding, topk,
+ * index_offset and the workspace (same queries) as for the f32 entry points. */
 int fbmm_bmm_x16(void* stream, const void* A, long long lda, long long stride_a,
                  const void* B, long long ldb, long long stride_b, int dtype,
                  void* C, long long ldc, long long stride_c, int l, int m, int n, int k);
@@ -187,12 +186,12 @@ int fbmm_mbmm_x16(void* stream, const void* A, long long lda, long long stride_a
                   const unsigned char* element_mask, int share_mask, int l, int m, int n, int k);
 int fbmm_min_bmm_x16(void* stream, const void* A, long long lda, long long stride_a,
                      const void* B, long long ldb, long long stride_b, int dtype,
-                     float* values, long long* indices, int l, int m, int n, int k, int dim,
+                     float* values, long long* indices, int l, int m, int n, int k, int dim, int distance,
                      void* workspace, size_t workspace_bytes);
 int fbmm_topk_bmm_x16(void* stream, const void* A, long long lda, long long stride_a,
                       const void* B, long long ldb, long long stride_b, int dtype,
                       float* values, long long* indices, int l, int m, int n, int k, int topk, int dim,
-                      long long index_offset, void* workspace, size_t workspace_bytes);
+                      int distance, long long index_offset, void* workspace, size_t workspace_bytes);
 
 /* k-means centroid update, the step that consumes min_bmm with FBMM_DIST_L2 (points as A,
  * centroids as the columns of B, dim = 2: `assignment` is its index output). For every

@@ -476,6 +476,24 @@ def test_mbmm_on_16_bit_operands(ops, dev, lib, dtype):
     device_ok(lib)
 
 
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_l2_distance_on_16_bit_operands(dev, lib, dtype):
+    """distance="l2" with 16-bit operands: norms of the 16-bit values in fp32, products on
+    the tensor cores; the oracle forms sum (a - b)^2 of the same values in fp64."""
+    from custom_matmul_kernels_b200 import MinBMMCUDA, TopkBMMCUDA
+    g = torch.Generator().manual_seed(29)
+    mn, tk = MinBMMCUDA(distance="l2"), TopkBMMCUDA(distance="l2")
+    for (l, m, k, n) in [(1, 300, 72, 700), (2, 130, 64, 257)]:
+        A = torch.randn(l, m, k, generator=g).to(dtype)
+        B = torch.randn(l, k, n, generator=g).to(dtype)
+        for dim in (1, 2):
+            v, i = mn(A.to(dev), B.to(dev), dim=dim)
+            R.check_min(v, i, A.float(), B.float(), dim, distance="l2")
+            tv, ti = tk(A.to(dev), B.to(dev), k=9, dim=dim)
+            R.check_topk(tv, ti, A.float(), B.float(), 9, dim, distance="l2")
+    assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
+
+
 def test_16_bit_exact_small_integers(ops, dev, lib):
     """Small-integer operands are exact in fp16 and bf16 and so is every partial sum: the
     16-bit kernels must return the fp32 kernels' values and indices bit for bit."""
