@@ -17,10 +17,15 @@
 //               keeps their bits)
 //   warps 6-9   epilogue: tcgen05.ld both accumulators, add them, then store / mask /
 //               reduce. One thread owns one output row, so per-row min and top-k state
-//               never crosses threads.
+//               never crosses threads (the mask epilogue, which keeps no state, runs
+//               warps 6-13, two per row quarter).
 //
 // Work is cut into units (batch, 128-row block, run of column tiles); CTA i processes
 // units i, i + gridDim.x, ... All four roles walk the same unit list.
+//
+// Variants (template parameters of the kernel): lo planes taken from global memory
+// instead of the splitters (PRESPLIT), clusters of two CTAs on 256-row blocks (PAIR), and
+// fp16 / bf16 operands multiplied as they are by kind::f16 (DT).
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
