@@ -186,6 +186,69 @@ def test_min_config4_slice_properties(ops, dev, lib):
     device_ok(lib)
 
 
+def test_min_config4_full_size_all_rows(ops, dev, lib):
+    """All 1 048 576 rows of configuration 4 against a chunked fp32 product (TF32 off) on the
+    same GPU: a test-only comparator that can afford every row, where the CPU oracle of the
+    previous test covers a sample. Values within the fp32 tolerance of both sides; where the
+    indices differ, the comparator's product at the returned index must be within tolerance
+    of its own minimum (a near-tie)."""
+    g = torch.Generator(device=dev).manual_seed(1004)
+    m, k, n = 1 << 20, 128, 65536
+    A = torch.randn(1, m, k, generator=g, device=dev)
+    B = torch.randn(1, k, n, generator=g, device=dev)
+    v, i = ops["min"](A, B, dim=2)
+    assert v.shape == (1, m) and i.dtype == torch.int64 and bool(((i >= 0) & (i < n)).all())
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        step, bad_val, bad_idx = 16384, 0, 0
+        for r0 in range(0, m, step):
+            C = A[0, r0:r0 + step] @ B[0]
+            wv, wi = C.min(dim=1)
+            gv, gi = v[0, r0:r0 + step], i[0, r0:r0 + step]
+            tol = 2 * (R.ATOL + R.RTOL * wv.abs())
+            bad_val += int(((gv - wv).abs() > tol).sum())
+            at = C.gather(1, gi[:, None])[:, 0]
+            bad_idx += int(((at - wv).abs() > tol).sum())
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert bad_val == 0 and bad_idx == 0, (bad_val, bad_idx)
+    device_ok(lib)
+
+
+def test_topk_config5_full_width_rows_against_gpu_reference(ops, dev, lib):
+    """2 048 rows of configuration 5 against all 1 048 576 columns (pre-split, repacked
+    planes, paced sweep), k = 64: descending values, unique in-range indices, and every
+    (value, index) pair reproduced by a chunked fp32 product (TF32 off) whose own top-64
+    values must agree within tolerance."""
+    g = torch.Generator(device=dev).manual_seed(1005)
+    m, k, n, kk = 2048, 256, 1 << 20, 64
+    A = torch.randn(1, m, k, generator=g, device=dev)
+    B = torch.randn(1, k, n, generator=g, device=dev)
+    v, i = ops["topk"](A, B, k=kk, dim=2)
+    assert bool((v[..., :-1] >= v[..., 1:]).all()) and bool(((i >= 0) & (i < n)).all())
+    srt = i.sort(dim=-1).values
+    assert bool((srt[..., 1:] != srt[..., :-1]).all())
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        best = torch.full((m, kk), float("-inf"), device=dev)
+        at = torch.empty(m, kk, device=dev)
+        cstep = 65536
+        for c0 in range(0, n, cstep):
+            C = A[0] @ B[0, :, c0:c0 + cstep]
+            best = torch.cat([best, C], dim=1).topk(kk, dim=1).values
+            inside = (i[0] >= c0) & (i[0] < c0 + cstep)
+            got = C.gather(1, (i[0] - c0).clamp(0, cstep - 1))
+            at = torch.where(inside, got, at)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    tol = 2 * (R.ATOL + R.RTOL * best.abs())
+    assert bool(((v[0] - best).abs() <= tol).all()), float((v[0] - best).abs().max())
+    assert bool(((at - v[0]).abs() <= tol).all()), "an index does not reproduce its value"
+    device_ok(lib)
+
+
 # ----------------------------------------------------------------------------- top-k
 def test_topk_exact_golden(ops, dev, lib):
     g = load_golden("exact_topk")
