@@ -96,6 +96,7 @@ int device_state(DeviceState** out) {
     if ((rc = set_smem_attr<kEpiStore, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiMask, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiMin, 1>()) != FBMM_OK) return rc;
+    if ((rc = set_smem_attr<kEpiTopk, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiTopk, 2>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiTopk, 4>()) != FBMM_OK) return rc;
     st.sms = prop.multiProcessorCount;
@@ -614,7 +615,7 @@ static void topk_plan(int l, int rows_per_batch, int cols, int sms, int* n_chunk
 // Running lists of the units in flight: one area per CTA (at most one CTA per SM), 32 E
 // entries x 128 rows of fp32 values and as many int32 columns.
 static size_t topk_scratch_bytes(int sms, int topk) {
-  const size_t list_slots = topk <= 64 ? 64 : 128;  // 32 E, as chosen at launch
+  const size_t list_slots = topk <= 32 ? 32 : (topk <= 64 ? 64 : 128);  // 32 E, as chosen at launch
   return static_cast<size_t>(sms) * list_slots * kTileM * 8;
 }
 
@@ -742,7 +743,8 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
       FBMM_CUDA(cudaMemsetAsync(pace_counts, 0, pp.count_bytes, stream));
     }
   }
-  if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch);  // list slots per lane
+  if (topk <= 32) rc = launch_gemm<kEpiTopk, 1>(stream, *st, p, s, e, lo_scratch);  // E: blocks of 32 list entries per row
+  else if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch);
   else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e, lo_scratch);
   if (rc != FBMM_OK) return rc;
   if (s.n_chunks > 1)
@@ -1151,7 +1153,8 @@ extern "C" int fbmm_topk_bmm_x16(void* stream_, const void* A, long long lda, lo
     own += norms_bytes(p);
   }
   e.topk_scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + own);
-  if (topk <= 64) rc = launch_gemm_x16<kEpiTopk, 2>(stream, *st, p, s, e, dtype);
+  if (topk <= 32) rc = launch_gemm_x16<kEpiTopk, 1>(stream, *st, p, s, e, dtype);
+  else if (topk <= 64) rc = launch_gemm_x16<kEpiTopk, 2>(stream, *st, p, s, e, dtype);
   else rc = launch_gemm_x16<kEpiTopk, 4>(stream, *st, p, s, e, dtype);
   if (rc != FBMM_OK) return rc;
   if (s.n_chunks > 1)

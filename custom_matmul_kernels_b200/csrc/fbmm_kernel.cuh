@@ -423,6 +423,41 @@ __device__ __noinline__ float topk_merge_own_rows(bool listed, int n_staged, flo
   __syncwarp();
   thread_sort32_desc(stg_own);
   FBMM_PROF_PHASE(0);
+  if (E == 1) {
+    // one block: it meets the candidates and is sorted in a single trip
+    float v[4][8];
+    int ix[4][8];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        v[c][e] = -INFINITY;
+        ix[c][e] = kTopkEmpty;
+        if (listed) {
+          v[c][e] = sv[(8 * c + e) * kTileM];
+          ix[c][e] = si[(8 * c + e) * kTileM];
+        }
+        const int2 cand = stg_own[(31 - (8 * c + e)) * kTileM];
+        if (topk_before(__int_as_float(cand.x), cand.y, v[c][e], ix[c][e])) {
+          v[c][e] = __int_as_float(cand.x);
+          ix[c][e] = cand.y;
+        }
+      }
+    }
+    topk_merge32_desc(v, ix);
+    float kth1 = -INFINITY;
+    const int at = (k - 1) & 31;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        sv[(8 * c + e) * kTileM] = v[c][e];
+        si[(8 * c + e) * kTileM] = ix[c][e];
+        if (8 * c + e == at) kth1 = v[c][e];
+      }
+    }
+    return kth1;
+  }
 #pragma unroll 1
   for (int c = 0; c < 4; ++c) {
     float v[E][8];
