@@ -1,21 +1,28 @@
 #!/usr/bin/env python
 """Benchmark of the fused-BMM hot path on N GPUs of one node.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5] [--impl reference]
 
-Prints ONE JSON line (rank 0). Workloads are the five benchmark configurations:
+Prints ONE JSON line (rank 0). The five benchmark configurations:
   c1 min_bmm  A[1,16384,64]    B[1,64,16384]            rows sharded
   c2 bmm      A[128,1024,128]  B[128,128,1024]          batches sharded
   c3 mbmm     A[128,1024,64]   B[128,64,1024] + mask    batches sharded
-  c4 min_bmm  A[1,1048576,128] B[1,128,65536]           rows sharded      (default)
+  c4 min_bmm  A[1,1048576,128] B[1,128,65536]           rows sharded
   c5 topk_bmm A[1,1048576,256] B[1,256,1048576], k=64   B columns sharded + all-gather + merge
-A step is one pass of the op over the whole configuration (strong scaling: the
-configuration is fixed, each rank takes its shard). Inputs are seeded synthetic tensors
-generated on the host. `value` is timed with the shard resident in HBM; `e2e` runs the
-same step through the Python wrapper from pinned host buffers, host<->device copies
-inside the timed region. `--impl reference` times the reference's semantics on the host
-cores (torch.bmm + min / topk / masked_fill, the reference's own test expressions) on a
-bounded sample of the same workload.
+The headline (`value`, `ms_per_step`, `roofline`, `e2e`) is the workload named by --workload,
+by default c5: the largest configuration that fits one GPU, and the one whose multi-GPU runs
+carry the data-path collective. The other four are measured in the same invocation and
+reported under `per_config`, each with its own step time, roofline, end-to-end figure, result
+check and (at one GPU) CPU baseline.
+
+A step is one pass of the op over the whole configuration (strong scaling: the configuration
+is fixed, each rank takes its shard). Inputs are seeded synthetic tensors generated on the
+host. `value` is timed with the shard resident in HBM; `e2e` runs the same step through the
+Python wrapper from pinned host buffers, host<->device copies inside the timed region.
+`check` compares a seeded sample of the timed outputs with the CPU oracle, outside the timed
+region. `--impl reference` times the reference's semantics on the host cores (torch.bmm +
+min / topk / masked_fill, the reference's own test expressions) on a bounded sample of the
+same workload.
 """
 from __future__ import annotations
 
@@ -44,7 +51,14 @@ SHAPES = {  # l, m, k, n
 }
 SEEDS = {"c1": 1001, "c2": 1002, "c3": 1003, "c4": 1004, "c5": 1005}
 OPS = {"c1": "min_bmm", "c2": "bmm", "c3": "mbmm", "c4": "min_bmm", "c5": "topk_bmm"}
+UNIT = {"c1": "rows/s", "c2": "batches/s", "c3": "batches/s", "c4": "rows/s", "c5": "rows/s"}
 TOPK = 64
+# Which measured cuBLAS figure a tensor-bound workload is held against: the sub-millisecond
+# kernels are timed one at a time with an L2 flush in between (burst); c4 and c5 run back to
+# back for seconds under the power cap (sustained). One yardstick per workload at every N;
+# both fractions are printed.
+SUSTAINED = {"c1": False, "c2": False, "c3": False, "c4": True, "c5": True}
+ARITHMETIC = "3xTF32 tensor-core products (tcgen05.mma kind::tf32), fp32 accumulation in TMEM"
 
 
 def env_int(name, default):
@@ -110,8 +124,8 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------
 def host_inputs(name, rank, world):
     """Seeded host tensors of this rank's shard (generated whole, then cut, so that every
-    world size sees the same configuration)."""
-    from custom_matmul_kernels_b200.sharding import shard_range
+    world size sees the same configuration). Rank 0 also keeps what its result check needs."""
+    from custom_matmul_kernels_b200.sharding import shard_range, shard_stride
     l, m, k, n = SHAPES[name]
     g = torch.Generator().manual_seed(SEEDS[name])
     out = {}
@@ -139,19 +153,33 @@ def host_inputs(name, rank, world):
         out["A"], out["B"] = A[:, r0:r1].contiguous(), B
         out["units"] = r1 - r0
         return out
-    # c5: columns of B sharded; generate per 64Ki-row / 64Ki-column pieces to bound host memory
+    # c5: columns of B sharded; B is generated in 64Ki-column pieces, every rank alike
     c0, c1 = shard_range(n, world, rank, 128)
     A = torch.randn(l, m, k, generator=g)
     B = torch.empty(l, k, c1 - c0)
+    sample_rows = check_rows("c5", m)
+    prod = torch.zeros(len(sample_rows), n, dtype=torch.float64) if rank == 0 else None
+    As = A[0, sample_rows].double() if rank == 0 else None
     piece = 65536
-    for p0 in range(0, n, piece):  # B is generated column-piece by column-piece, every rank alike
+    for p0 in range(0, n, piece):
         blk = torch.randn(l, k, min(piece, n - p0), generator=g)
         lo, hi = max(p0, c0), min(p0 + blk.shape[2], c1)
         if lo < hi:
             B[:, :, lo - c0:hi - c0] = blk[:, :, lo - p0:hi - p0]
+        if rank == 0:  # the oracle's fp64 product of the sampled rows against ALL columns, piece by piece
+            prod[:, p0:p0 + blk.shape[2]] = As @ blk[0].double()
     out["A"], out["B"], out["col0"] = A, B, c0
+    out["cols_per_rank"] = shard_stride(n, world, 128)
     out["units"] = m
+    out["check_product"] = prod
     return out
+
+
+def check_rows(name, m):
+    """Seeded sample of output rows the result check looks at."""
+    count = {"c1": 512, "c4": 256, "c5": 48}[name]
+    g = torch.Generator().manual_seed(SEEDS[name] + 77)
+    return torch.randperm(m, generator=g)[:min(count, m)].sort().values
 
 
 # ---------------------------------------------------------------------------------------
@@ -171,6 +199,9 @@ class Workload:
         self.B = self.B_pin.to(dev)
         self.in_bytes = self.A.numel() * 4 + self.B.numel() * 4
         self.kernels_per_step = 1
+        self.phase_events = []
+        l_, m_, k_ = self.A.shape
+        n_ = self.B.shape[2]
         if name == "c3":
             self.masks = make_masks(h["mask"].to(dev))
             self.masks_pin = tuple(t.cpu().pin_memory() for t in self.masks)
@@ -181,20 +212,18 @@ class Workload:
         elif name in ("c1", "c4"):
             self.op = MinBMMCUDA()
             self.kernels_per_step = 2   # fused GEMM+min kernel, key-unpack kernel
-            l_, m_, k_ = self.A.shape
-            n_ = self.B.shape[2]
-            if self.op.lib.fbmm_presplit_workspace_bytes(l_, m_, n_, k_, ord("n"), k_, m_ * k_, ord("n"), n_, k_ * n_):
+            if self.op.lib.fbmm_presplit_workspace_bytes(l_, m_, n_, k_, 2, ord("n"), k_, m_ * k_, ord("n"), n_, k_ * n_):
                 self.kernels_per_step += 1  # lo-plane pass over B (A is split in shared memory)
         else:
             self.op = TopkBMMCUDA()
             self.kernels_per_step = 1 + (1 if world > 1 else 0)  # + candidate merge
-            l_, m_, k_ = self.A.shape
-            n_ = self.B.shape[2]
-            if self.op.lib.fbmm_presplit_workspace_bytes(l_, m_, n_, k_, ord("n"), k_, m_ * k_, ord("n"), n_, k_ * n_):
+            if n_ > 0 and self.op.lib.fbmm_presplit_workspace_bytes(l_, m_, n_, k_, 2, ord("n"), k_, m_ * k_, ord("n"), n_,
+                                                                    k_ * n_):
                 self.kernels_per_step += 2 if k_ > 128 else 1  # plane passes over B and, when it streams, A
         self.out_host = None
+        self.last = None
 
-    def run(self, A, B, masks=None):
+    def run(self, A, B, masks=None, timings=None):
         n = self.name
         if n == "c2":
             return (self.op(A, B),)
@@ -202,11 +231,17 @@ class Workload:
             return (self.op(A, B, *(masks or self.masks)),)
         if n in ("c1", "c4"):
             return self.op(A, B, dim=2)
+        if self.world == 1:
+            return self.op(A, B, k=TOPK, dim=2)
         return self.sharding.topk_bmm_column_sharded(
-            A, B, self.h["col0"], TOPK, lambda a, b, k, off: self.op(a, b, k=k, dim=2, index_offset=off))
+            A, B, self.h["cols_per_rank"], TOPK, lambda a, b, k: self.op.packed(a, b, k=k, dim=2), timings=timings)
 
     def step(self):
-        return self.run(self.A, self.B)
+        timings = {} if (self.name == "c5" and self.world > 1) else None
+        self.last = self.run(self.A, self.B, timings=timings)
+        if timings:
+            self.phase_events.append(timings["events"])
+        return self.last
 
     def e2e_step(self):
         self.A.copy_(self.A_pin, non_blocking=True)
@@ -226,6 +261,71 @@ class Workload:
     def out_bytes(self):
         return sum(h.numel() * h.element_size() for h in (self.out_host or []))
 
+    # ---- result check against the CPU oracle (outside every timed region)
+    def check(self):
+        """Compares a seeded sample of this rank's last timed output with the oracle's fp64
+        product. Returns counts; `unexplained` > 0 means a value outside rel 1e-5 / abs 1e-4
+        or an index that does not point at a (near-)extremal entry."""
+        from oracle import ref_semantics as R
+        n = self.name
+        outs = [o.detach() for o in self.last]
+        res = {"max_abs_err": 0.0, "max_err_over_tol": 0.0, "index_mismatches": 0, "unexplained": 0, "checked": ""}
+        try:
+            if n in ("c2", "c3"):
+                C = outs[0]
+                picks = sorted({0, C.shape[0] // 2, C.shape[0] - 1}) if C.shape[0] else []
+                for b in picks:
+                    want = torch.mm(self.h["A"][b].double(), self.h["B"][b].double())
+                    if n == "c3":
+                        want.masked_fill_(~self.h["mask"][b], 0)
+                        if bool((C[b].cpu()[~self.h["mask"][b]] != 0).any()):
+                            res["unexplained"] += 1
+                    err = (C[b].cpu().double() - want).abs()
+                    tol = R.ATOL + R.RTOL * want.abs()
+                    res["max_abs_err"] = max(res["max_abs_err"], float(err.max()))
+                    res["max_err_over_tol"] = max(res["max_err_over_tol"], float((err / tol).max()))
+                    res["unexplained"] += int((err > tol).sum())
+                res["checked"] = f"{len(picks)} batches of this rank's shard, every element"
+            elif n in ("c1", "c4"):
+                v, i = outs
+                rows = check_rows(n, v.shape[1])
+                C = self.h["A"][0, rows].double() @ self.h["B"][0].double()
+                wv, wi = C.min(dim=1)
+                gv, gi = v[0].cpu()[rows].double(), i[0].cpu()[rows]
+                tol = R.ATOL + R.RTOL * wv.abs()
+                err = (gv - wv).abs()
+                at = C.gather(1, gi.clamp(0, C.shape[1] - 1)[:, None])[:, 0]
+                res["max_abs_err"] = float(err.max())
+                res["max_err_over_tol"] = float((err / tol).max())
+                res["index_mismatches"] = int((gi != wi).sum())
+                res["unexplained"] = int((err > tol).sum()) + int(((at - wv).abs() > tol).sum()) + int(
+                    ((gi < 0) | (gi >= C.shape[1])).sum())
+                res["checked"] = f"{len(rows)} rows of this rank's shard against all {C.shape[1]} columns"
+            else:
+                if self.rank != 0:
+                    return res
+                v, i = outs
+                rows = check_rows("c5", v.shape[1])
+                C = self.h["check_product"]
+                wv, wi = C.topk(TOPK, dim=1)
+                gv, gi = v[0].cpu()[rows].double(), i[0].cpu()[rows]
+                tol = R.ATOL + R.RTOL * wv.abs()
+                err = (gv - wv).abs()
+                inr = (gi >= 0) & (gi < C.shape[1])
+                at = C.gather(1, gi.clamp(0, C.shape[1] - 1))
+                dup = (gi.sort(dim=1).values[:, 1:] == gi.sort(dim=1).values[:, :-1])
+                res["max_abs_err"] = float(err.max())
+                res["max_err_over_tol"] = float((err / tol).max())
+                res["index_mismatches"] = int((gi != wi).sum())
+                res["unexplained"] = int((err > tol).sum()) + int(((at - gv).abs() > tol).sum()) + int((~inr).sum()) + int(
+                    dup.sum()) + int((gv[:, :-1] < gv[:, 1:]).sum())
+                res["checked"] = (f"{len(rows)} rows of the {'merged ' if self.world > 1 else ''}result against all "
+                                  f"{C.shape[1]} columns, all {TOPK} entries")
+        except Exception as e:  # noqa: BLE001 -- a broken check must show up in the line, not kill the bench
+            res["unexplained"] += 1
+            res["error"] = repr(e)
+        return res
+
 
 def timed_steps(fn, steps, flush):
     """K steps, each bracketed by CUDA events on the current stream; an L2 flush (outside
@@ -241,8 +341,36 @@ def timed_steps(fn, steps, flush):
     return [a.elapsed_time(b) for a, b in ev]
 
 
+def back_to_back_ms(fn, steps):
+    """K enqueues under ONE event pair (no flush in between): launch latency amortised."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def sync_each_ms(fn, steps):
+    """Wall clock with a device synchronisation after every call, as the reference's harness
+    times (colab/test_minbmm.ipynb:2123-2134)."""
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+        torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / steps * 1e3
+
+
+_tf32_live = None
+
+
 def measure_tf32_cublas():
     """cuBLAS TF32 throughput (fp32 torch.matmul with TF32 allowed, 8192^3, best of 10)."""
+    global _tf32_live
+    if _tf32_live is not None:
+        return _tf32_live
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = True
     try:
@@ -257,7 +385,8 @@ def measure_tf32_cublas():
             torch.cuda.synchronize()
             if i >= 3:
                 best = min(best, e0.elapsed_time(e1))
-        return 2 * 8192 ** 3 / best / 1e9
+        _tf32_live = 2 * 8192 ** 3 / best / 1e9
+        return _tf32_live
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
 
@@ -272,38 +401,41 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16": 1590.0, "bf16_sustained": 1400.0, "source": "fallback"}
 
 
-def algorithmic_bytes(name, units):
-    """Compulsory HBM bytes of one launch over `units` rows/batches of this rank."""
+def algorithmic_bytes(name, units, n_cols):
+    """Compulsory HBM bytes of one launch over `units` rows/batches (and n_cols columns) of this rank."""
     l, m, k, n = SHAPES[name]
     if name == "c2":
         return units * (m * k + k * n + m * n) * 4
     if name == "c3":
         return units * ((m * k + k * n + m * n) * 4 + (m // 128) * (n // 128) + (m // 8) * (n // 8))
     if name in ("c1", "c4"):
-        return units * k * 4 + k * n * 4 + units * 12
-    return units * k * 4 + k * n * 4 + units * TOPK * 12
+        return units * k * 4 + k * n_cols * 4 + units * 12
+    return units * k * 4 + k * n_cols * 4 + units * TOPK * 12
 
 
 def measured_traffic(name, units):
-    """DRAM bytes per launch from the ncu capture summarised in profiles/ (c4 min kernel at
-    262 144 rows: 352.3 MB read + 5.4 MB written), scaled by the rows processed: B's hi and lo
-    planes (67.1 MB) are read once per launch whatever the row count; the rest (A, read once
-    per column range = twice, and the outputs) grows with the rows. None where no capture
-    has been taken."""
-    if name != "c4":
-        return None
-    b_planes = 2 * 128 * 65536 * 4
-    per_row = (352.28288e6 + 5.39648e6 - b_planes) / 262144.0
-    return b_planes + units * per_row
+    """DRAM bytes per launch from the ncu captures summarised in profiles/, scaled by the units
+    processed; None where no capture has been taken.
+    c4 (min kernel at 262 144 rows: 352.3 MB read + 5.4 MB written): B's hi and lo planes
+    (67.1 MB) are read once per launch whatever the row count; the rest (A, read once per
+    column range = twice, and the outputs) grows with the rows."""
+    if name == "c4":
+        b_planes = 2 * 128 * 65536 * 4
+        per_row = (352.28288e6 + 5.39648e6 - b_planes) / 262144.0
+        return b_planes + units * per_row
+    return TRAFFIC_PER_UNIT.get(name, lambda u: None)(units)
 
 
-def cpu_baseline(name):
+# per-launch DRAM traffic of the c2 / c3 kernels from the captures in profiles/ (bytes per batch)
+TRAFFIC_PER_UNIT = {}
+
+
+def cpu_baseline(name, budget_s):
     """Reference semantics on the host cores over a bounded sample (rank 0, N=1)."""
     from oracle import ref_semantics as R
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     l, m, k, n = SHAPES[name]
-    t_budget = 10.0
     if name in ("c1", "c4"):
         rows = 8192 if name == "c4" else 16384
         d = R.make_inputs(name, rows=rows)
@@ -311,7 +443,7 @@ def cpu_baseline(name):
         fn()
         t0 = time.perf_counter()
         reps = 0
-        while time.perf_counter() - t0 < t_budget:
+        while time.perf_counter() - t0 < budget_s:
             fn()
             reps += 1
         dt = (time.perf_counter() - t0) / reps
@@ -334,7 +466,7 @@ def cpu_baseline(name):
     fn()
     t0 = time.perf_counter()
     reps = 0
-    while time.perf_counter() - t0 < t_budget:
+    while time.perf_counter() - t0 < budget_s:
         fn()
         reps += 1
     dt = (time.perf_counter() - t0) / reps
@@ -342,15 +474,144 @@ def cpu_baseline(name):
             "sample": f"{batches} of {l} batches, torch.bmm{' + masked_fill' if name == 'c3' else ''} on CPU, mean of {reps} passes"}
 
 
-UNIT = {"c1": "rows/s", "c2": "batches/s", "c3": "batches/s", "c4": "rows/s", "c5": "rows/s"}
-
-
-def config_dict(name, world, flush):
+def config_dict(name, world):
+    """The same for both arms: what is computed, on what, cut how."""
     l, m, k, n = SHAPES[name]
     part = {"c1": "A rows", "c4": "A rows", "c2": "batches", "c3": "batches", "c5": "B columns + all-gather"}[name]
     return {"workload": f"{name}: {OPS[name]} A[{l},{m},{k}] B[{l},{k},{n}]" + (f" k={TOPK}" if name == "c5" else ""),
-            "sharding": f"{part} over {world} GPU(s)", "precision": "fp32 in/out, 3xTF32 tensor-core products",
-            "l2": "flushed between steps" if flush else "inputs exceed L2"}
+            "sharding": f"{part} over {world} GPU(s)", "precision": "fp32 in, fp32 out",
+            "l2": "flushed between steps" if name in ("c1", "c2", "c3") else "inputs exceed L2"}
+
+
+def roofline(name, wl, ms_mean, peaks, world):
+    """Roofline record of the dominant kernel (the fused GEMM) of this rank's launch."""
+    l, m, k, n = SHAPES[name]
+    n_cols = wl.B.shape[2]
+    units = wl.h["units"]
+    if name in ("c2", "c3"):
+        flops = 2.0 * units * m * n * k
+    else:
+        flops = 2.0 * units * n_cols * k
+    nbytes = algorithmic_bytes(name, units, n_cols)
+    burst = peaks["bf16"] / 2 / 3
+    sustained = peaks["bf16_sustained"] / 2 / 3
+    tensor_time = flops / (burst * 1e12)
+    hbm_time = nbytes / (peaks["hbm_gbs"] * 1e9)
+    achieved_tflops = flops / (ms_mean / 1e3) / 1e12 if ms_mean > 0 else 0.0
+    achieved_gbs = nbytes / (ms_mean / 1e3) / 1e9 if ms_mean > 0 else 0.0
+    roof = {}
+    if hbm_time > tensor_time:
+        roof.update({"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "peak_note": f"{peaks['source']} STREAM-style copy"})
+    else:
+        use_sustained = SUSTAINED[name]
+        roof.update({"bound": "tensor", "achieved": achieved_tflops, "peak": sustained if use_sustained else burst,
+                     "unit": "TFLOP/s",
+                     "peak_note": f"{peaks['source']} cuBLAS bf16 {'sustained' if use_sustained else 'burst'} / 2 (tf32) / 3 "
+                                  "(three tf32 MMAs per fp32 product)"})
+    roof["frac"] = roof["achieved"] / roof["peak"] if roof["peak"] else None
+    roof["tensor"] = {"achieved_tflops": achieved_tflops, "frac_burst": achieved_tflops / burst,
+                      "frac_sustained": achieved_tflops / sustained, "frac_mma_issue_ceiling": achieved_tflops / 341.0}
+    roof["hbm"] = {"achieved_gbs": achieved_gbs, "frac": achieved_gbs / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
+    roof["ideal_ms"] = {"tensor_burst": tensor_time * 1e3, "hbm": hbm_time * 1e3}
+    roof["traffic"] = measured_traffic(name, units)
+    roof["kernel"] = "fbmm_gemm_kernel"
+    return roof
+
+
+def measure(name, args, rank, local_rank, world, dev, headline):
+    """One workload: warm-up, K device-timed steps, the end-to-end leg, the result check."""
+    import torch.distributed as dist
+    wl = Workload(name, rank, world, dev)
+    small = name in ("c1", "c2", "c3")
+    flush = torch.zeros(L2_BYTES * 2 // 4, device=dev) if small else None
+    steps = args.steps if (headline or not small) else max(args.steps, 50)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        wl.step()
+    barrier()
+    wl.phase_events = []
+    sampler = None
+    if rank == 0 and headline:
+        sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
+                               os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+        sampler.start()
+    ms = timed_steps(wl.step, steps, flush)
+    barrier()
+    phases = None
+    if wl.phase_events:
+        acc = [0.0, 0.0, 0.0]
+        for ev in wl.phase_events:
+            for j in range(3):
+                acc[j] += ev[j].elapsed_time(ev[j + 1])
+        phases = {"local_topk_ms": acc[0] / len(wl.phase_events), "all_gather_ms": acc[1] / len(wl.phase_events),
+                  "merge_ms": acc[2] / len(wl.phase_events)}
+    check = wl.check()
+    extra = {}
+    if small and not args.no_e2e:
+        extra["ms_back_to_back"] = back_to_back_ms(wl.step, steps)
+        extra["ms_sync_each"] = sync_each_ms(wl.step, steps)
+        barrier()
+    # end to end: pinned host -> device -> op -> pinned host, every step
+    if args.no_e2e:
+        ms_e2e = [float("nan")] * steps
+    else:
+        for _ in range(2):
+            wl.e2e_step()
+        barrier()
+        ms_e2e = timed_steps(wl.e2e_step, steps, None)
+        barrier()
+    clocks = sampler.stop() if sampler is not None else None
+
+    tot = torch.tensor([sum(ms), sum(ms_e2e), check["max_abs_err"], check["max_err_over_tol"]], device=dev,
+                       dtype=torch.float64)
+    cnt = torch.tensor([check["index_mismatches"], check["unexplained"]], device=dev, dtype=torch.int64)
+    if world > 1:
+        dist.all_reduce(tot, op=dist.ReduceOp.MAX)
+        dist.all_reduce(cnt, op=dist.ReduceOp.SUM)
+    total_ms, total_e2e_ms = float(tot[0]), float(tot[1])
+    l, m, k, n = SHAPES[name]
+    units_total = l if name in ("c2", "c3") else m
+    rec = None
+    if rank == 0:
+        ms_per_step = total_ms / steps
+        peaks = load_peaks()
+        roof = roofline(name, wl, statistics.mean(ms), peaks, world)
+        if world == 1:
+            roof["tf32_cublas_tflops_live"] = measure_tf32_cublas()
+            roof["tensor"]["frac_live_tf32"] = roof["tensor"]["achieved_tflops"] / (roof["tf32_cublas_tflops_live"] / 3)
+        check_out = dict(check)
+        check_out.update({"max_abs_err": float(tot[2]), "max_err_over_tol": float(tot[3]),
+                          "index_mismatches": int(cnt[0]), "unexplained": int(cnt[1]),
+                          "ok": int(cnt[1]) == 0, "ranks": world,
+                          "tolerance": "rel 1e-5 / abs 1e-4 against the fp64 product of the CPU oracle"})
+        rec = {
+            "metric": f"fused {OPS[name]} throughput ({name})", "value": units_total / (ms_per_step / 1e3),
+            "unit": UNIT[name], "steps": steps, "ms_per_step": ms_per_step,
+            "ms_per_step_median": statistics.median(ms), "ms_per_step_best": min(ms),
+            "tflops": 2.0 * l * m * n * k / (ms_per_step / 1e3) / 1e12,
+            "config": config_dict(name, world),
+            "e2e": {"value": units_total / (total_e2e_ms / steps / 1e3), "unit": UNIT[name],
+                    "h2d_bytes_per_step": wl.in_bytes, "d2h_bytes_per_step": wl.out_bytes(),
+                    "note": "bytes are this rank's; every rank copies its own shard"},
+            "gpu_launches": wl.kernels_per_step * steps * world,
+            "roofline": roof, "check": check_out,
+        }
+        rec.update(extra)
+        if phases:
+            rec["phases_rank0"] = phases
+        if clocks is not None:
+            rec["clocks"] = clocks
+        if world == 1 and not args.no_cpu:
+            rec["cpu_baseline"] = cpu_baseline(name, 10.0 if headline else 4.0)
+    del wl, flush
+    torch.cuda.empty_cache()
+    return rec
 
 
 def run_ours(args):
@@ -361,87 +622,28 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     name = args.workload
-    wl = Workload(name, rank, world, dev)
-    flush = None
-    if wl.in_bytes < 2 * L2_BYTES:
-        flush = torch.zeros(L2_BYTES * 2 // 4, device=dev)
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        wl.step()
-    barrier()
-    sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
-                           os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank])
+    head = measure(name, args, rank, local_rank, world, dev, True)
+    per = {}
+    if not args.no_per_config:
+        for other in sorted(SHAPES):
+            if other != name:
+                per[other] = measure(other, args, rank, local_rank, world, dev, False)
     if rank == 0:
-        sampler.start()
-    ms = timed_steps(wl.step, args.steps, flush)
-    barrier()
-    # end to end: pinned host -> device -> op -> pinned host, every step
-    if args.no_e2e:
-        ms_e2e = [float("nan")] * args.steps
-    else:
-        for _ in range(2):
-            wl.e2e_step()
-        barrier()
-        ms_e2e = timed_steps(wl.e2e_step, args.steps, None)
-        barrier()
-    clocks = sampler.stop() if rank == 0 else None
-
-    tot = torch.tensor([sum(ms), sum(ms_e2e)], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(tot, op=dist.ReduceOp.MAX)
-    total_ms, total_e2e_ms = float(tot[0]), float(tot[1])
-    l, m, k, n = SHAPES[name]
-    units_total = l if name in ("c2", "c3") else m
-    if rank == 0:
-        ms_per_step = total_ms / args.steps
-        value = units_total / (ms_per_step / 1e3)
-        peaks = load_peaks()
-        # dominant kernel of this rank: the fused GEMM; the step's other kernels (key
-        # unpack, candidate merge) are a few microseconds and ride inside the same events
-        launch_ms = statistics.mean(ms)
-        flops_launch = 2.0 * (wl.h["units"] if name not in ("c2", "c3") else wl.h["units"] * m) * n * k
-        if name == "c5":
-            flops_launch = 2.0 * m * wl.B.shape[2] * k
-        bytes_launch = algorithmic_bytes(name, wl.h["units"]) if name != "c5" else (
-            m * k * 4 + k * wl.B.shape[2] * 4 + m * TOPK * 12)
-        tensor_time = flops_launch * 3 / ((peaks["bf16"] / 2) * 1e12)
-        hbm_time = bytes_launch / (peaks["hbm_gbs"] * 1e9)
-        if hbm_time > tensor_time:
-            roof = {"bound": "hbm", "achieved": bytes_launch / (launch_ms / 1e3) / 1e9, "peak": peaks["hbm_gbs"],
-                    "unit": "GB/s"}
-        else:
-            sustained = total_ms > 500.0
-            peak = (peaks["bf16_sustained"] if sustained else peaks["bf16"]) / 2 / 3
-            roof = {"bound": "tensor", "achieved": flops_launch / (launch_ms / 1e3) / 1e12, "peak": peak,
-                    "unit": "TFLOP/s",
-                    "peak_note": f"{peaks['source']} cuBLAS bf16 {'sustained' if sustained else 'burst'} / 2 (tf32) / 3 "
-                                 "(three tf32 MMAs per fp32 product)"}
-        roof["frac"] = roof["achieved"] / roof["peak"]
-        roof["traffic"] = measured_traffic(name, wl.h["units"])
-        roof["kernel"] = "fbmm_gemm_kernel"
-        if world == 1:
-            roof["tf32_cublas_tflops_live"] = measure_tf32_cublas()
         line = {
-            "metric": f"fused {OPS[name]} throughput ({name})", "value": value, "unit": UNIT[name], "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": config_dict(name, world, flush is not None),
-            "tflops": 2.0 * l * m * n * k / (ms_per_step / 1e3) / 1e12,
-            "e2e": {"value": units_total / (total_e2e_ms / args.steps / 1e3), "unit": UNIT[name],
-                    "h2d_bytes_per_step": wl.in_bytes, "d2h_bytes_per_step": wl.out_bytes(),
-                    "note": "bytes are this rank's; every rank copies its own shard"},
-            "gpu_launches": wl.kernels_per_step * args.steps * world,
-            "clocks": clocks, "roofline": roof,
+            "metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "arithmetic": ARITHMETIC,
         }
+        for key in ("config", "tflops", "e2e", "gpu_launches", "clocks", "roofline", "check", "phases_rank0",
+                    "ms_per_step_median", "ms_per_step_best", "ms_back_to_back", "ms_sync_each", "cpu_baseline"):
+            if key in head:
+                line[key] = head[key]
+        if per:
+            line["per_config"] = per
+            line["gpu_launches"] += sum(p["gpu_launches"] for p in per.values())
         if args.rows is not None or args.batches is not None:
             line["reduced"] = True
-        if world == 1 and not args.no_cpu:
-            line["cpu_baseline"] = cpu_baseline(name)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -488,7 +690,8 @@ def run_reference(args):
         "impl": "reference", "metric": f"fused {OPS[name]} throughput ({name})", "value": value, "unit": UNIT[name],
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 1), "ms_per_step": dt * 1e3,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": config_dict(name, world, False),
+        "arithmetic": "fp32 on the host cores (torch CPU)",
+        "config": config_dict(name, world),
         "cpu_baseline": {"value": value, "unit": UNIT[name], "cores": cores, "kind": "port",
                          "sample": sample + "; torch CPU restatement of the reference's test expressions "
                                             "(the reference's kernels need CuPy and a GPU)"},
@@ -502,23 +705,26 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--workload", default="c4", choices=sorted(SHAPES))
+    ap.add_argument("--workload", default="c5", choices=sorted(SHAPES))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--no-per-config", action="store_true", help="measure the headline workload only")
     ap.add_argument("--rows", type=int, default=None,
                     help="profiling only: cut c1/c4/c5 to this many rows of A (the line is marked reduced)")
     ap.add_argument("--batches", type=int, default=None,
                     help="profiling only: cut c2/c3 to this many batches (the line is marked reduced)")
-    ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the end-to-end leg")
+    ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the end-to-end legs")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"c1": 50, "c2": 30, "c3": 30, "c4": 10, "c5": 2}[args.workload]
+        args.steps = {"c1": 50, "c2": 30, "c3": 30, "c4": 10, "c5": 4}[args.workload]
     if args.rows is not None and args.workload in ("c1", "c4", "c5"):
         l, m, k, n = SHAPES[args.workload]
         SHAPES[args.workload] = (l, args.rows, k, n)
     if args.batches is not None and args.workload in ("c2", "c3"):
         l, m, k, n = SHAPES[args.workload]
         SHAPES[args.workload] = (args.batches, m, k, n)
+    if args.rows is not None or args.batches is not None:
+        args.no_per_config = True
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -23,16 +23,6 @@ class BMMCUDA(CustomKernel):
         self.patch_m = patch_m
         self.patch_n = patch_n
 
-    def get_mode(self, A, B):
-        """Stride layout of the last two dims, as bmm.py:56-66."""
-        mode = [None, None]
-        for i, X in enumerate((A, B)):
-            if X.stride()[-1] == 1:
-                mode[i] = "n"
-            elif X.stride()[-2] == 1:
-                mode[i] = "t"
-        return "".join(m or "?" for m in mode)
-
     def __call__(self, A, B):
         A3, B3, two_d = self.check_inputs(A, B, (torch.float32,) + _X16)
         l, m, k = A3.shape

@@ -139,13 +139,61 @@ int check_operand(const char* name, const Operand& op, int k, int l) {
   if (l > 1 && (op.stride & 3) != 0)
     return fail(FBMM_ERR_ALIGN, "%s batch stride %lld is not a multiple of 4 elements", name, op.stride);
   if (l > 1 && op.stride < 0) return fail(FBMM_ERR_INVALID, "%s batch stride is negative", name);
+  // a batch stride of 0 with l > 1 is a broadcast: one matrix serves every batch
   return FBMM_OK;
 }
 
+bool is_broadcast(const Operand& op, int l) { return l > 1 && op.stride == 0; }
+
 // 3-D tiled tensor map over one operand. K-major: dims (k, rows, l), box (32, box_rows, 1),
 // 128-byte swizzle. MN-major: dims (rows, k, l), box (32, 32, 1), 128-byte swizzle with
-// 32-byte atoms (the only MN-major layout tcgen05 takes for tf32).
+// 32-byte atoms (the only MN-major layout tcgen05 takes for tf32). A broadcast operand
+// (batch stride 0) is described as a single batch; the kernel then asks for batch 0 only.
+//
+// Encoding a map costs a driver call, and a serving loop calls with the same buffers over
+// and over, so the last few maps are kept, keyed by everything that goes into them.
+struct TensorMapKey {
+  const void* ptr;
+  long long ld, stride;
+  int rows, k, l, box_rows, kind;  // kind: 0 fp32 K-major, 1 fp32 MN-major, 2 fp16, 3 bf16
+  bool operator==(const TensorMapKey& o) const {
+    return ptr == o.ptr && ld == o.ld && stride == o.stride && rows == o.rows && k == o.k && l == o.l &&
+           box_rows == o.box_rows && kind == o.kind;
+  }
+};
+constexpr int kTensorMapCacheSize = 32;
+struct TensorMapCache {
+  TensorMapKey keys[kTensorMapCacheSize];
+  CUtensorMap maps[kTensorMapCacheSize];
+  int used = 0, next = 0;
+  unsigned long long hits = 0, misses = 0;
+};
+std::mutex g_tm_mu;
+TensorMapCache g_tm_cache;
+
+bool tensor_map_lookup(const TensorMapKey& key, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_tm_mu);
+  for (int i = 0; i < g_tm_cache.used; ++i)
+    if (g_tm_cache.keys[i] == key) {
+      *out = g_tm_cache.maps[i];
+      ++g_tm_cache.hits;
+      return true;
+    }
+  ++g_tm_cache.misses;
+  return false;
+}
+void tensor_map_remember(const TensorMapKey& key, const CUtensorMap& map) {
+  std::lock_guard<std::mutex> lock(g_tm_mu);
+  const int at = g_tm_cache.next;
+  g_tm_cache.keys[at] = key;
+  g_tm_cache.maps[at] = map;
+  g_tm_cache.next = (at + 1) % kTensorMapCacheSize;
+  if (g_tm_cache.used < kTensorMapCacheSize) ++g_tm_cache.used;
+}
+
 int make_tensor_map(CUtensorMap* map, const Operand& op, int k, int l, int box_rows) {
+  const TensorMapKey key{op.ptr, op.ld, l > 1 ? op.stride : 0, op.rows, k, l, box_rows, op.mn_major ? 1 : 0};
+  if (tensor_map_lookup(key, map)) return FBMM_OK;
   cuuint64_t dims[3];
   cuuint32_t box[3];
   if (op.mn_major) {
@@ -157,17 +205,18 @@ int make_tensor_map(CUtensorMap* map, const Operand& op, int k, int l, int box_r
     dims[1] = static_cast<cuuint64_t>(op.rows);
     box[0] = 32; box[1] = static_cast<cuuint32_t>(box_rows);
   }
-  dims[2] = static_cast<cuuint64_t>(l);
+  const bool one_batch = l == 1 || is_broadcast(op, l);
+  dims[2] = one_batch ? 1u : static_cast<cuuint64_t>(l);
   box[2] = 1;
   const cuuint64_t pitch_bytes = static_cast<cuuint64_t>(op.ld) * 4u;
-  cuuint64_t strides[2] = {pitch_bytes, l > 1 ? static_cast<cuuint64_t>(op.stride) * 4u : pitch_bytes * dims[1]};
-  if (strides[1] == 0) strides[1] = pitch_bytes;  // broadcast batch: any legal value, coordinate stays 0
+  cuuint64_t strides[2] = {pitch_bytes, one_batch ? pitch_bytes * dims[1] : static_cast<cuuint64_t>(op.stride) * 4u};
   cuuint32_t elem_strides[3] = {1, 1, 1};
   const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float*>(op.ptr), dims, strides,
                               box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                               op.mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(FBMM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  tensor_map_remember(key, *map);
   return FBMM_OK;
 }
 
@@ -379,6 +428,7 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
       ob_hi.stride = static_cast<long long>(p.N) * kp;
       ob_lo = ob_hi;
       shape.b_mn = 0;
+      shape.b_bcast = 0;  // the repacked planes hold one copy per batch
     } else {
       fbmm_split_lo_kernel<<<blocks, threads, 0, stream>>>(p.b.ptr, b_lo, span_b);
     }
@@ -436,6 +486,8 @@ GemmShape base_shape(const RowProblem& p) {
   s.L = p.L; s.M = p.M; s.N = p.N; s.K = p.K;
   s.a_mn = p.a.mn_major ? 1 : 0;
   s.b_mn = p.b.mn_major ? 1 : 0;
+  s.a_bcast = is_broadcast(p.a, p.L) ? 1 : 0;
+  s.b_bcast = is_broadcast(p.b, p.L) ? 1 : 0;
   const int rows_per_block = use_pairs(p.M) ? 2 * kTileM : kTileM;
   s.m_blocks = (p.M + rows_per_block - 1) / rows_per_block;
   s.n_tiles = (p.N + kTileN - 1) / kTileN;
@@ -593,13 +645,13 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   return FBMM_OK;
 }
 
-size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k, int a_layout, long long lda, long long stride_a,
-                                     int b_layout, long long ldb, long long stride_b) {
+size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k, int dim, int a_layout, long long lda,
+                                     long long stride_a, int b_layout, long long ldb, long long stride_b) {
   if (l <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
   RowProblem p;
-  if (make_row_problem(&p, nullptr, a_layout, lda, stride_a, nullptr, b_layout, ldb, stride_b, l, m, n, k, 2) != FBMM_OK)
+  if (make_row_problem(&p, nullptr, a_layout, lda, stride_a, nullptr, b_layout, ldb, stride_b, l, m, n, k, dim) != FBMM_OK)
     return 0;
-  if (p.a.ld < (p.a.mn_major ? m : k) || p.b.ld < (p.b.mn_major ? n : k)) return 0;
+  if (p.a.ld < (p.a.mn_major ? p.M : k) || p.b.ld < (p.b.mn_major ? p.N : k)) return 0;
   if (!presplit_worthwhile(p)) return 0;
   return presplit_bytes(p);
 }
@@ -655,19 +707,34 @@ size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int d
   return need;
 }
 
-int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long* cand_indices, int groups,
-                        long long rows, int topk, float* out_values, long long* out_indices);
+}  // extern "C"
 
-int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
-                      int b_layout, long long ldb, long long stride_b, float* values, long long* indices, int l, int m,
-                      int n, int k, int topk, int dim, int distance, long long index_offset, void* workspace,
-                      size_t workspace_bytes) {
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+namespace {
+
+// Inputs and outputs of the candidate merge: lists either as two arrays (fp32 values, int64
+// indices) or as one array of packed 8-byte pairs (value bits, int32 index; -1 = empty).
+struct MergeIO {
+  const float* cv;
+  const long long* ci;
+  const int2* cp;                // packed input; the index of group g gets g * group_index_stride added
+  long long group_index_stride;
+  float* ov;
+  long long* oi;
+  int2* op;                      // packed output (indices must fit 31 bits)
+};
+int launch_topk_merge(cudaStream_t stream, const MergeIO& io, int groups, long long rows, int topk);
+
+// topk_bmm behind fbmm_topk_bmm_f32 (values + int64 indices with index_offset added) and
+// fbmm_topk_bmm_packed_f32 (`packed` set: 8-byte pairs with plain int32 column indices).
+int topk_bmm_impl(cudaStream_t stream, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
+                  int b_layout, long long ldb, long long stride_b, float* values, long long* indices, int2* packed, int l,
+                  int m, int n, int k, int topk, int dim, int distance, long long index_offset, void* workspace,
+                  size_t workspace_bytes) {
   int rc;
   if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
   if ((rc = check_distance(distance)) != FBMM_OK) return rc;
   if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
-  if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
+  if (packed == nullptr && (values == nullptr || indices == nullptr)) return fail(FBMM_ERR_INVALID, "values or indices is null");
   RowProblem p;
   if ((rc = make_row_problem(&p, A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
   if ((rc = check_operand("A", dim == 2 ? p.a : p.b, k, l)) != FBMM_OK) return rc;
@@ -696,6 +763,7 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
   } else {
     e.topk_values = values;
     e.topk_indices = indices;
+    e.topk_packed = packed;
     e.topk_chunk_rows = 0;
   }
   size_t own = 0;
@@ -747,12 +815,36 @@ int fbmm_topk_bmm_f32(void* stream_, const float* A, int a_layout, long long lda
   else if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch);
   else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e, lo_scratch);
   if (rc != FBMM_OK) return rc;
-  if (s.n_chunks > 1)
-    return fbmm_topk_merge_f32(stream_, e.topk_values, e.topk_indices, s.n_chunks, rows, topk, values, indices);
+  if (s.n_chunks > 1) {
+    MergeIO io{};
+    io.cv = e.topk_values; io.ci = e.topk_indices;
+    io.ov = values; io.oi = indices; io.op = packed;
+    return launch_topk_merge(stream, io, s.n_chunks, rows, topk);
+  }
   return FBMM_OK;
 }
 
-}  // extern "C"
+}  // namespace
+
+extern "C" int fbmm_topk_bmm_f32(void* stream, const float* A, int a_layout, long long lda, long long stride_a,
+                                 const float* B, int b_layout, long long ldb, long long stride_b, float* values,
+                                 long long* indices, int l, int m, int n, int k, int topk, int dim, int distance,
+                                 long long index_offset, void* workspace, size_t workspace_bytes) {
+  return topk_bmm_impl(static_cast<cudaStream_t>(stream), A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, values,
+                       indices, nullptr, l, m, n, k, topk, dim, distance, index_offset, workspace, workspace_bytes);
+}
+
+extern "C" int fbmm_topk_bmm_packed_f32(void* stream, const float* A, int a_layout, long long lda, long long stride_a,
+                                        const float* B, int b_layout, long long ldb, long long stride_b,
+                                        void* candidates, int l, int m, int n, int k, int topk, int dim, int distance,
+                                        void* workspace, size_t workspace_bytes) {
+  if (candidates == nullptr) return fail(FBMM_ERR_INVALID, "candidates is null");
+  if ((reinterpret_cast<uintptr_t>(candidates) & 7u) != 0) return fail(FBMM_ERR_ALIGN, "candidates is not 8-byte aligned");
+  // index_offset stays 0: packed indices are plain columns of this call's B
+  return topk_bmm_impl(static_cast<cudaStream_t>(stream), A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, nullptr,
+                       nullptr, static_cast<int2*>(candidates), l, m, n, k, topk, dim, distance, 0, workspace,
+                       workspace_bytes);
+}
 
 // ---------------------------------------------------------------------------------------
 // candidate merge (one warp per row)
@@ -762,12 +854,16 @@ namespace fbmm {
 // One warp per row. The running list stays in registers (striped over the lanes); every
 // group's list is already sorted, so it is merged whole by topk_merge_lists, and skipped
 // when its best entry cannot beat the current k-th value. Entries carry their source slot
-// (group * k + position) instead of the 64-bit index, which is fetched at the end; equal
-// values therefore keep the order (group, position), which is ascending index order when
-// the groups cover ascending index ranges.
+// (group * k + position) instead of the index, which is fetched at the end; equal values
+// therefore keep the order (group, position), which is ascending index order when the
+// groups cover ascending index ranges. Lists come as two arrays (fp32 values, int64 indices)
+// or as packed pairs (value bits, int32 index local to the group's column range, to which
+// group * group_index_stride is added); the result goes out in either form.
 template <int E>
 __global__ void __launch_bounds__(128) fbmm_topk_merge_kernel(const float* __restrict__ cv, const long long* __restrict__ ci,
-                                                              int groups, long long rows, int k, float* ov, long long* oi) {
+                                                              const int2* __restrict__ cp, long long group_index_stride,
+                                                              int groups, long long rows, int k, float* ov, long long* oi,
+                                                              int2* op) {
   const long long row = static_cast<long long>(blockIdx.x) * 4 + (threadIdx.x >> 5);
   if (row >= rows) return;  // whole warps leave together
   const int lane = static_cast<int>(lane_id());
@@ -777,8 +873,7 @@ __global__ void __launch_bounds__(128) fbmm_topk_merge_kernel(const float* __res
   for (int j = 0; j < E; ++j) { L[j] = -INFINITY; LI[j] = kTopkEmpty; }
   float thr = -INFINITY;
   for (int g = 0; g < groups; ++g) {
-    const float* gv = cv + (static_cast<long long>(g) * rows + row) * k;
-    const long long* gi = ci + (static_cast<long long>(g) * rows + row) * k;
+    const long long base = (static_cast<long long>(g) * rows + row) * k;
     float G[E];
     int GI[E];
 #pragma unroll
@@ -786,45 +881,89 @@ __global__ void __launch_bounds__(128) fbmm_topk_merge_kernel(const float* __res
       const int i = j * 32 + lane;
       G[j] = -INFINITY;
       GI[j] = kTopkEmpty;
-      if (i < k && gi[i] >= 0) { G[j] = gv[i]; GI[j] = g * k + i; }
+      if (i < k) {
+        if (cp != nullptr) {
+          const int2 e = cp[base + i];
+          if (e.y >= 0) { G[j] = __int_as_float(e.x); GI[j] = g * k + i; }
+        } else if (ci[base + i] >= 0) {
+          G[j] = cv[base + i];
+          GI[j] = g * k + i;
+        }
+      }
     }
     const float g0 = __shfl_sync(0xffffffffu, G[0], 0);
     if (g > 0 && !(g0 > thr)) continue;  // sorted: nothing in this group can enter
     topk_merge_lists<E>(L, LI, G, GI);
     thr = topk_list_entry<E>(L, k - 1);
   }
-  float* lv = ov + row * k;
-  long long* li = oi + row * k;
 #pragma unroll
   for (int j = 0; j < E; ++j) {
     const int i = j * 32 + lane;
     if (i < k) {
-      lv[i] = L[j];
       long long id = -1;
-      if (LI[j] != kTopkEmpty) id = ci[(static_cast<long long>(LI[j] / k) * rows + row) * k + (LI[j] % k)];
-      li[i] = id;
+      if (LI[j] != kTopkEmpty) {
+        const int g = LI[j] / k;
+        const long long at = (static_cast<long long>(g) * rows + row) * k + (LI[j] % k);
+        id = cp != nullptr ? static_cast<long long>(cp[at].y) + g * group_index_stride : ci[at];
+      }
+      if (op != nullptr) {
+        op[row * k + i] = make_int2(__float_as_int(L[j]), static_cast<int>(id));
+      } else {
+        ov[row * k + i] = L[j];
+        oi[row * k + i] = id;
+      }
     }
   }
 }
 
+// Fills a packed candidate buffer with empty entries (-inf, -1): what a rank whose column
+// shard is empty contributes to the exchange.
+__global__ void fbmm_fill_empty_candidates_kernel(int2* out, long long count) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < count) out[i] = make_int2(__float_as_int(-INFINITY), -1);
+}
+
 }  // namespace fbmm
 
-extern "C" int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long* cand_indices, int groups,
-                                   long long rows, int topk, float* out_values, long long* out_indices) {
-  if (cand_values == nullptr || cand_indices == nullptr || out_values == nullptr || out_indices == nullptr)
-    return fail(FBMM_ERR_INVALID, "a pointer is null");
+namespace {
+int launch_topk_merge(cudaStream_t stream, const MergeIO& io, int groups, long long rows, int topk) {
   if (groups <= 0 || rows <= 0) return fail(FBMM_ERR_INVALID, "groups and rows must be positive");
   if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
   if (groups > (1 << 23)) return fail(FBMM_ERR_INVALID, "at most %d groups", 1 << 23);  // slot ids stay below 2^31
   const long long blocks = (rows + 3) / 4;
   if (blocks > 0x7fffffffll) return fail(FBMM_ERR_INVALID, "too many rows");
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned grid = static_cast<unsigned>(blocks);
   if (topk <= 64)
-    fbmm::fbmm_topk_merge_kernel<2><<<static_cast<unsigned>(blocks), 128, 0, s>>>(cand_values, cand_indices, groups, rows, topk, out_values, out_indices);
+    fbmm::fbmm_topk_merge_kernel<2><<<grid, 128, 0, stream>>>(io.cv, io.ci, io.cp, io.group_index_stride, groups, rows,
+                                                              topk, io.ov, io.oi, io.op);
   else
-    fbmm::fbmm_topk_merge_kernel<4><<<static_cast<unsigned>(blocks), 128, 0, s>>>(cand_values, cand_indices, groups, rows, topk, out_values, out_indices);
+    fbmm::fbmm_topk_merge_kernel<4><<<grid, 128, 0, stream>>>(io.cv, io.ci, io.cp, io.group_index_stride, groups, rows,
+                                                              topk, io.ov, io.oi, io.op);
   FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
+}
+}  // namespace
+
+extern "C" int fbmm_topk_merge_f32(void* stream, const float* cand_values, const long long* cand_indices, int groups,
+                                   long long rows, int topk, float* out_values, long long* out_indices) {
+  if (cand_values == nullptr || cand_indices == nullptr || out_values == nullptr || out_indices == nullptr)
+    return fail(FBMM_ERR_INVALID, "a pointer is null");
+  MergeIO io{};
+  io.cv = cand_values; io.ci = cand_indices; io.ov = out_values; io.oi = out_indices;
+  return launch_topk_merge(static_cast<cudaStream_t>(stream), io, groups, rows, topk);
+}
+
+extern "C" int fbmm_topk_merge_packed_f32(void* stream, const void* candidates, int groups, long long rows, int topk,
+                                          long long group_index_stride, float* out_values, long long* out_indices) {
+  if (candidates == nullptr || out_values == nullptr || out_indices == nullptr)
+    return fail(FBMM_ERR_INVALID, "a pointer is null");
+  if ((reinterpret_cast<uintptr_t>(candidates) & 7u) != 0) return fail(FBMM_ERR_ALIGN, "candidates is not 8-byte aligned");
+  if (group_index_stride < 0) return fail(FBMM_ERR_INVALID, "group_index_stride is negative");
+  MergeIO io{};
+  io.cp = static_cast<const int2*>(candidates);
+  io.group_index_stride = group_index_stride;
+  io.ov = out_values; io.oi = out_indices;
+  return launch_topk_merge(static_cast<cudaStream_t>(stream), io, groups, rows, topk);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -849,7 +988,8 @@ extern "C" int fbmm_kmeans_update_f32(void* stream_, const float* X, long long l
   int rc;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   float* sums = static_cast<float*>(workspace);
-  float* counts = reinterpret_cast<float*>(static_cast<char*>(workspace) + align_up(static_cast<size_t>(k) * d * 4, 256));
+  unsigned int* counts =
+      reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + align_up(static_cast<size_t>(k) * d * 4, 256));
   FBMM_CUDA(cudaMemsetAsync(workspace, 0, need, stream));
   const int threads = 256;
   const size_t part_bytes = (static_cast<size_t>(k) * d + k) * sizeof(float);
@@ -871,9 +1011,7 @@ extern "C" int fbmm_kmeans_update_f32(void* stream_, const float* X, long long l
   }
   const long long total = static_cast<long long>(k) * d;
   fbmm::fbmm_kmeans_finalize_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0, stream>>>(
-      sums, counts, centroids, ldc, d, total);
-  if (counts_out != nullptr)
-    FBMM_CUDA(cudaMemcpyAsync(counts_out, counts, static_cast<size_t>(k) * 4, cudaMemcpyDeviceToDevice, stream));
+      sums, counts, centroids, ldc, d, total, counts_out);
   FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
 }
@@ -976,17 +1114,21 @@ int check_operand_x16(const char* name, const Operand& op, int k, int l) {
 // K-major tensor map over 2-byte elements: dims (k, rows, l), box (64, box_rows, 1), i.e.
 // 128 bytes per row, 128-byte swizzle. Pitches in `op` count elements.
 int make_tensor_map_x16(CUtensorMap* map, const Operand& op, int k, int l, int box_rows, int dtype) {
-  cuuint64_t dims[3] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(op.rows), static_cast<cuuint64_t>(l)};
+  const TensorMapKey key{op.ptr, op.ld, l > 1 ? op.stride : 0, op.rows, k, l, box_rows, dtype == FBMM_BF16 ? 3 : 2};
+  if (tensor_map_lookup(key, map)) return FBMM_OK;
+  const bool one_batch = l == 1 || is_broadcast(op, l);
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(op.rows),
+                        one_batch ? 1u : static_cast<cuuint64_t>(l)};
   cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
   const cuuint64_t pitch_bytes = static_cast<cuuint64_t>(op.ld) * 2u;
-  cuuint64_t strides[2] = {pitch_bytes, l > 1 ? static_cast<cuuint64_t>(op.stride) * 2u : pitch_bytes * dims[1]};
-  if (strides[1] == 0) strides[1] = pitch_bytes;
+  cuuint64_t strides[2] = {pitch_bytes, one_batch ? pitch_bytes * dims[1] : static_cast<cuuint64_t>(op.stride) * 2u};
   cuuint32_t elem_strides[3] = {1, 1, 1};
   const CUresult r = g_encode(map, dtype == FBMM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                               3, const_cast<float*>(op.ptr), dims, strides, box, elem_strides,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(FBMM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  tensor_map_remember(key, *map);
   return FBMM_OK;
 }
 
@@ -1217,4 +1359,222 @@ extern "C" int fbmm_mbmm_x16(void* stream_, const void* A, long long lda, long l
   e.tm_stride = share_mask ? 0 : static_cast<long long>((m + 7) / 8) * e.tm_cols;
   e.em_stride = share_mask ? 0 : static_cast<long long>(m) * n;
   return launch_gemm_x16<kEpiMask, 1>(stream, *st, p, s, e, dtype);
+}
+
+// ---------------------------------------------------------------------------------------
+// Column-sharded top-k behind the C ABI: local top-k -> one NCCL all-gather of packed
+// candidates -> merge. NCCL is reached through dlopen, so the library has no link-time
+// dependency on it and a process that never shards never loads it. If the process already
+// holds a libnccl.so.2 (a PyTorch process does), the dynamic loader hands back that copy,
+// so communicators made by the host's own NCCL calls and by fbmm_comm_init_rank agree.
+// ---------------------------------------------------------------------------------------
+#include <dlfcn.h>
+
+namespace {
+
+struct NcclUniqueId { char internal[128]; };  // ncclUniqueId: 128 opaque bytes
+typedef int (*NcclGetUniqueIdFn)(NcclUniqueId*);
+typedef int (*NcclCommInitRankFn)(void**, int, NcclUniqueId, int);
+typedef int (*NcclCommDestroyFn)(void*);
+typedef int (*NcclAllGatherFn)(const void*, void*, size_t, int, void*, cudaStream_t);
+typedef int (*NcclAllReduceFn)(const void*, void*, size_t, int, int, void*, cudaStream_t);
+typedef const char* (*NcclGetErrorStringFn)(int);
+constexpr int kNcclInt32 = 2, kNcclInt64 = 4, kNcclMax = 2;  // ncclDataType_t / ncclRedOp_t values
+
+struct NcclApi {
+  void* handle = nullptr;
+  NcclGetUniqueIdFn get_unique_id = nullptr;
+  NcclCommInitRankFn comm_init_rank = nullptr;
+  NcclCommDestroyFn comm_destroy = nullptr;
+  NcclAllGatherFn all_gather = nullptr;
+  NcclAllReduceFn all_reduce = nullptr;
+  NcclGetErrorStringFn error_string = nullptr;
+};
+std::mutex g_nccl_mu;
+NcclApi g_nccl;
+
+int nccl_api(NcclApi** out) {
+  std::lock_guard<std::mutex> lock(g_nccl_mu);
+  if (g_nccl.handle == nullptr) {
+    const char* name = getenv("FBMM_NCCL_LIB");
+    if (name == nullptr || name[0] == '\0') name = "libnccl.so.2";
+    void* h = dlopen(name, RTLD_NOW | RTLD_LOCAL);
+    if (h == nullptr) return fail(FBMM_ERR_COMM, "cannot load %s: %s", name, dlerror());
+    NcclApi api;
+    api.get_unique_id = reinterpret_cast<NcclGetUniqueIdFn>(dlsym(h, "ncclGetUniqueId"));
+    api.comm_init_rank = reinterpret_cast<NcclCommInitRankFn>(dlsym(h, "ncclCommInitRank"));
+    api.comm_destroy = reinterpret_cast<NcclCommDestroyFn>(dlsym(h, "ncclCommDestroy"));
+    api.all_gather = reinterpret_cast<NcclAllGatherFn>(dlsym(h, "ncclAllGather"));
+    api.all_reduce = reinterpret_cast<NcclAllReduceFn>(dlsym(h, "ncclAllReduce"));
+    api.error_string = reinterpret_cast<NcclGetErrorStringFn>(dlsym(h, "ncclGetErrorString"));
+    if (!api.get_unique_id || !api.comm_init_rank || !api.comm_destroy || !api.all_gather || !api.all_reduce ||
+        !api.error_string) {
+      dlclose(h);
+      return fail(FBMM_ERR_COMM, "%s lacks an NCCL entry point this library needs", name);
+    }
+    api.handle = h;
+    g_nccl = api;
+  }
+  *out = &g_nccl;
+  return FBMM_OK;
+}
+
+#define FBMM_NCCL(api, call)                                                                         \
+  do {                                                                                               \
+    const int r_ = (call);                                                                           \
+    if (r_ != 0) return fail(FBMM_ERR_COMM, "%s: %s", #call, (api)->error_string(r_));               \
+  } while (0)
+
+struct ShardedLayout {
+  size_t send_off, recv_off, status_off, local_off, total;
+};
+ShardedLayout sharded_layout(int world, int m, int topk, size_t local_bytes) {
+  ShardedLayout lay;
+  const size_t list = align_up(static_cast<size_t>(m) * topk * 8, 256);
+  lay.send_off = 0;
+  lay.recv_off = list;
+  lay.status_off = lay.recv_off + (world > 1 ? static_cast<size_t>(world) * list : 0);
+  lay.local_off = lay.status_off + 256;
+  lay.total = lay.local_off + align_up(local_bytes, 256);
+  return lay;
+}
+
+}  // namespace
+
+extern "C" int fbmm_comm_get_unique_id(void* id128) {
+  if (id128 == nullptr) return fail(FBMM_ERR_INVALID, "id128 is null");
+  NcclApi* api;
+  int rc;
+  if ((rc = nccl_api(&api)) != FBMM_OK) return rc;
+  FBMM_NCCL(api, api->get_unique_id(static_cast<NcclUniqueId*>(id128)));
+  return FBMM_OK;
+}
+
+extern "C" int fbmm_comm_init_rank(void** comm, int world, int rank, const void* id128) {
+  if (comm == nullptr || id128 == nullptr) return fail(FBMM_ERR_INVALID, "comm or id128 is null");
+  if (world <= 0 || rank < 0 || rank >= world) return fail(FBMM_ERR_INVALID, "bad rank %d of %d", rank, world);
+  NcclApi* api;
+  int rc;
+  if ((rc = nccl_api(&api)) != FBMM_OK) return rc;
+  NcclUniqueId id;
+  memcpy(&id, id128, sizeof(id));
+  FBMM_NCCL(api, api->comm_init_rank(comm, world, id, rank));
+  return FBMM_OK;
+}
+
+extern "C" int fbmm_comm_destroy(void* comm) {
+  if (comm == nullptr) return FBMM_OK;
+  NcclApi* api;
+  int rc;
+  if ((rc = nccl_api(&api)) != FBMM_OK) return rc;
+  FBMM_NCCL(api, api->comm_destroy(comm));
+  return FBMM_OK;
+}
+
+extern "C" size_t fbmm_topk_bmm_sharded_workspace_bytes(int world, int m, int n_local, int k, int topk, int distance,
+                                                        int a_layout, long long lda, int b_layout, long long ldb) {
+  if (world <= 0 || m <= 0 || k <= 0 || topk <= 0 || n_local < 0) return 0;
+  size_t local = 0;
+  if (n_local > 0)
+    local = align_up(fbmm_topk_bmm_workspace_bytes(1, m, n_local, k, topk, 2, distance), 256) +
+            fbmm_presplit_workspace_bytes(1, m, n_local, k, 2, a_layout, lda, 0, b_layout, ldb, 0);
+  return sharded_layout(world, m, topk, local).total;
+}
+
+extern "C" int fbmm_topk_bmm_sharded_f32(void* stream_, void* comm, int world, int rank, const float* A, int a_layout,
+                                         long long lda, const float* B_local, int b_layout, long long ldb,
+                                         long long cols_per_rank, float* values, long long* indices, int m, int n_local,
+                                         int k, int topk, int distance, int check_peers, void* workspace,
+                                         size_t workspace_bytes) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (world <= 0 || rank < 0 || rank >= world) return fail(FBMM_ERR_INVALID, "bad rank %d of %d", rank, world);
+  if (world > 1 && comm == nullptr) return fail(FBMM_ERR_INVALID, "comm is null");
+  if (m <= 0 || k <= 0 || n_local < 0) return fail(FBMM_ERR_INVALID, "m, k must be positive and n_local >= 0, got %d %d %d", m, k, n_local);
+  if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
+  if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
+  if (cols_per_rank < n_local) return fail(FBMM_ERR_INVALID, "cols_per_rank %lld is smaller than n_local %d", cols_per_rank, n_local);
+  if (cols_per_rank * world > 0x7ffffffell) return fail(FBMM_ERR_INVALID, "global column indices must stay below 2^31 - 1");
+  // Checks that come out the same on every rank (they depend on world, m and topk only) fail
+  // here, on all ranks alike. Whatever can differ from rank to rank -- the local operands,
+  // the local part of the workspace -- is folded into local_rc below and, with check_peers,
+  // exchanged before any rank commits to the all-gather.
+  const ShardedLayout lay = sharded_layout(world, m, topk, 0);
+  if (workspace == nullptr || workspace_bytes < lay.local_off)
+    return fail(FBMM_ERR_WORKSPACE, "sharded topk_bmm needs at least %zu workspace bytes for the exchange buffers, got %zu",
+                lay.local_off, workspace_bytes);
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
+  NcclApi* api = nullptr;
+  int rc;
+  if (world > 1 && (rc = nccl_api(&api)) != FBMM_OK) return rc;
+  char* ws = static_cast<char*>(workspace);
+  int2* send = reinterpret_cast<int2*>(ws + lay.send_off);
+  int2* recv = world > 1 ? reinterpret_cast<int2*>(ws + lay.recv_off) : send;
+  int* status = reinterpret_cast<int*>(ws + lay.status_off);
+  const long long entries = static_cast<long long>(m) * topk;
+
+  // 1. this rank's candidates, written in wire format straight into the send buffer
+  int local_rc = FBMM_OK;
+  const size_t need = fbmm_topk_bmm_sharded_workspace_bytes(world, m, n_local, k, topk, distance, a_layout, lda, b_layout, ldb);
+  if (workspace_bytes < need) {
+    local_rc = fail(FBMM_ERR_WORKSPACE, "sharded topk_bmm needs %zu workspace bytes on this rank, got %zu", need, workspace_bytes);
+  } else if (n_local > 0) {
+    local_rc = topk_bmm_impl(stream, A, a_layout, lda, 0, B_local, b_layout, ldb, 0, nullptr, nullptr, send, 1, m, n_local,
+                             k, topk, 2, distance, 0, ws + lay.local_off, workspace_bytes - lay.local_off);
+  } else {
+    fbmm::fbmm_fill_empty_candidates_kernel<<<static_cast<unsigned>((entries + 255) / 256), 256, 0, stream>>>(send, entries);
+    if (cudaGetLastError() != cudaSuccess) local_rc = fail(FBMM_ERR_CUDA, "fill kernel launch failed");
+  }
+  // 2. optional agreement that every rank got this far: a rank that failed must not leave
+  //    the others waiting inside the all-gather
+  if (world > 1 && check_peers) {
+    char saved[sizeof(g_err)];
+    memcpy(saved, g_err, sizeof(saved));
+    FBMM_CUDA(cudaMemsetAsync(status, local_rc == FBMM_OK ? 0 : 1, sizeof(int), stream));
+    FBMM_NCCL(api, api->all_reduce(status, status, 1, kNcclInt32, kNcclMax, comm, stream));
+    int any = 0;
+    FBMM_CUDA(cudaMemcpyAsync(&any, status, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    FBMM_CUDA(cudaStreamSynchronize(stream));
+    if (local_rc != FBMM_OK) { memcpy(g_err, saved, sizeof(saved)); return local_rc; }
+    if (any != 0) return fail(FBMM_ERR_PEER, "another rank failed before the candidate exchange; nothing was merged");
+  } else if (local_rc != FBMM_OK) {
+    return local_rc;
+  }
+  // 3. one all-gather of the packed lists, 4. merge with global column indices
+  if (world > 1) FBMM_NCCL(api, api->all_gather(send, recv, static_cast<size_t>(entries), kNcclInt64, comm, stream));
+  MergeIO io{};
+  io.cp = recv;
+  io.group_index_stride = cols_per_rank;
+  io.ov = values; io.oi = indices;
+  return launch_topk_merge(stream, io, world, m, topk);
+}
+
+// ---------------------------------------------------------------------------------------
+// self-test of the bounded-wait path
+// ---------------------------------------------------------------------------------------
+namespace fbmm {
+// One warp waits on an mbarrier that nobody ever arrives on, with a budget of `budget`
+// cycles. The wait runs out, the warp leaves the way the fused kernel's roles do (shared
+// abort flag, then bit 0 of the device status word) and the kernel returns normally.
+__global__ void fbmm_wait_expiry_selftest_kernel(long long budget) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(&bar, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  (void)mbar_wait(&bar, 0, &abort_flag, budget);
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag != 0) atomicOr(&g_fbmm_status[0], 1u);
+}
+}  // namespace fbmm
+
+extern "C" int fbmm_selftest_wait_expiry(void* stream) {
+  DeviceState* st;
+  int rc;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  fbmm::fbmm_wait_expiry_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(200000LL);
+  FBMM_CUDA(cudaGetLastError());
+  return FBMM_OK;
 }

@@ -11,10 +11,10 @@
 //   warps 2-5   splitters: lo = x - tf32(x), written beside the raw tile (the raw tile
 //               itself serves as the hi plane because the tensor core ignores the low
 //               13 mantissa bits of a tf32 operand)
-//   warp 1      MMA issuer: per 8-wide k-step three tcgen05.mma kind::tf32
-//               (lo*hi and hi*lo into a "small" TMEM accumulator, hi*hi into a "big"
-//               one; TMEM accumulation truncates, and keeping the small terms apart
-//               keeps their bits)
+//   warp 1      MMA issuer: per 8-wide k-step two tcgen05.mma kind::tf32: A_hi x [B_hi | B_lo]
+//               (N = 256: hi*hi lands in a "big" TMEM accumulator and hi*lo in a "small" one
+//               beside it) and A_lo x B_hi (N = 128, into the small one). TMEM accumulation
+//               truncates, and keeping the small terms apart keeps their bits
 //   warps 6-9   epilogue: tcgen05.ld both accumulators, add them, then store / mask /
 //               reduce. One thread owns one output row, so per-row min and top-k state
 //               never crosses threads (the mask epilogue, which keeps no state, runs
@@ -96,6 +96,7 @@ struct GemmShape {
   int L, M, N, K;
   int a_mn;  // A stored [l][k][m] (m contiguous) instead of [l][m][k]
   int b_mn;  // B stored [l][k][n] (n contiguous) instead of [l][n][k]
+  int a_bcast, b_bcast;  // the operand has one matrix that serves every batch (batch stride 0)
   int m_blocks;         // ceil(M / 128)
   int n_tiles;          // ceil(N / TILE_N)
   int n_chunks;         // column chunks per row block
@@ -135,6 +136,9 @@ struct EpiArgs {
   long long topk_chunk_rows;  // rows between the lists of consecutive column chunks (0: one chunk)
   float* topk_scratch;        // running lists of the unit a CTA works on: per CTA 32 E entries x 128 rows of
                               // values, then as many int32 columns, entry-major (see topk_merge_own_rows)
+  int2* topk_packed;          // when set, the lists are written here instead of topk_values / topk_indices:
+                              // [L][M][k] pairs (value bits, int32 column WITHOUT index_offset; -1 = empty),
+                              // the wire format of the column-sharded exchange
   // squared-l2 distance (min / top-k): squared norms of the row operand [L][M] and of the
   // column operand [L][N]; null for the inner product
   const float* row_norms;
@@ -549,7 +553,7 @@ __device__ __noinline__ float topk_merge_own_rows(bool listed, int n_staged, flo
 // the row-wise writes and the entry-wise reads spread over the banks, and the global
 // stores run along the entries of one row. `rows_valid`: rows of this warp that exist.
 __device__ __forceinline__ void topk_write_out(const float* sv, const int* si, int k, long long index_offset,
-                                               float* lv0, long long* li0, int rows_valid, int2* stg_w) {
+                                               float* lv0, long long* li0, int2* lp0, int rows_valid, int2* stg_w) {
   const int lane = static_cast<int>(lane_id());
   for (int e0 = 0; e0 < k; e0 += 32) {
 #pragma unroll 8
@@ -560,8 +564,12 @@ __device__ __forceinline__ void topk_write_out(const float* sv, const int* si, i
 #pragma unroll 4
       for (int r = 0; r < rows_valid; ++r) {
         const int2 e = stg_w[lane * kTileM + ((r + lane) & 31)];
-        lv0[static_cast<long long>(r) * k + e0 + lane] = __int_as_float(e.x);
-        li0[static_cast<long long>(r) * k + e0 + lane] = (e.y == kTopkEmpty) ? -1ll : static_cast<long long>(e.y) + index_offset;
+        if (lp0 != nullptr) {
+          lp0[static_cast<long long>(r) * k + e0 + lane] = make_int2(e.x, e.y == kTopkEmpty ? -1 : e.y);
+        } else {
+          lv0[static_cast<long long>(r) * k + e0 + lane] = __int_as_float(e.x);
+          li0[static_cast<long long>(r) * k + e0 + lane] = (e.y == kTopkEmpty) ? -1ll : static_cast<long long>(e.y) + index_offset;
+        }
       }
     }
     __syncwarp();
@@ -781,6 +789,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   };
   // this CTA's 128 rows of A, k-block kb
   auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int mb, int b) {
+    if (shape.a_bcast) b = 0;
     if (!shape.a_mn) {
       tma_issue(dst, map, bar, to_leader, kb * kKElems, row_base(mb), b, a_policy);
     } else {
@@ -792,6 +801,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // this CTA's columns of B tile t (all 128, or its 64 of a pair), k-block kb
   auto load_b = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int t, int b) {
     const int col = t * TILE_N + static_cast<int>(cta_rank) * kBCols;
+    if (shape.b_bcast) b = 0;
     if (!shape.b_mn) {
       tma_issue(dst, map, bar, to_leader, kb * kKElems, col, b, kL2EvictLast);
     } else {
@@ -1090,8 +1100,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // output lists of this warp's first row (rows of a warp are consecutive)
       const long long warp_row0 = (shape.tiles_per_chunk > 0 ? (t0 / shape.tiles_per_chunk) : 0) * epi.topk_chunk_rows +
                                   static_cast<long long>(b) * shape.M + row_base(mb) + static_cast<int>(quarter) * 32;
-      float* lv0 = (EPI == kEpiTopk) ? epi.topk_values + warp_row0 * epi.k : nullptr;
-      long long* li0 = (EPI == kEpiTopk) ? epi.topk_indices + warp_row0 * epi.k : nullptr;
+      const bool packed_out = (EPI == kEpiTopk) && epi.topk_packed != nullptr;
+      float* lv0 = (EPI == kEpiTopk && !packed_out) ? epi.topk_values + warp_row0 * epi.k : nullptr;
+      long long* li0 = (EPI == kEpiTopk && !packed_out) ? epi.topk_indices + warp_row0 * epi.k : nullptr;
+      int2* lp0 = packed_out ? epi.topk_packed + warp_row0 * epi.k : nullptr;
       int2* stg_w = stg + quarter * 32;
       // running list of this lane's row in the CTA's scratch area
       float* sv = nullptr;
@@ -1397,7 +1409,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             topk_merge_own_rows<TOPK_E>(has_list, n_staged, sv, si, epi.k, stg + row_in_tile);
           __syncwarp();
           const int rows_valid = min(32, shape.M - (row_base(mb) + static_cast<int>(quarter) * 32));
-          topk_write_out(sv, si, epi.k, epi.index_offset, lv0, li0, rows_valid, stg_w);
+          topk_write_out(sv, si, epi.k, epi.index_offset, lv0, li0, lp0, rows_valid, stg_w);
         }
       }
     }
@@ -1518,13 +1530,14 @@ __global__ void fbmm_min_finalize_kernel(const unsigned long long* __restrict__ 
 }
 
 // k-means centroid update, the step after min_bmm with the l2 distance has assigned every
-// point to its nearest centroid: sums[c][:] += X[i][:] and counts[c] += 1 for c = assign[i].
+// point to its nearest centroid: sums[c][:] += X[i][:] and counts[c] += 1 for c = assign[i]
+// (integer counts: exact for any number of points).
 // One warp per point; the additions are fire-and-forget reductions that resolve in L2,
 // where the k x d sums live. Summation order, and with it the last bits of the result,
 // varies from run to run. Points with an assignment outside [0, k) are skipped.
 __global__ void fbmm_kmeans_accumulate_kernel(const float* __restrict__ x, long long ldx,
                                               const long long* __restrict__ assign, long long n, int d, int k,
-                                              float* __restrict__ sums, float* __restrict__ counts) {
+                                              float* __restrict__ sums, unsigned int* __restrict__ counts) {
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const int lane = static_cast<int>(threadIdx.x & 31u);
@@ -1534,7 +1547,7 @@ __global__ void fbmm_kmeans_accumulate_kernel(const float* __restrict__ x, long 
     const float* row = x + i * ldx;
     float* dst = sums + c * d;
     for (int j = lane; j < d; j += 32) atomicAdd(dst + j, row[j]);
-    if (lane == 0) atomicAdd(counts + c, 1.f);
+    if (lane == 0) atomicAdd(counts + c, 1u);
   }
 }
 
@@ -1544,8 +1557,9 @@ __global__ void fbmm_kmeans_accumulate_kernel(const float* __restrict__ x, long 
 // contended additions stay on chip.
 __global__ void fbmm_kmeans_accumulate_smem_kernel(const float* __restrict__ x, long long ldx,
                                                    const long long* __restrict__ assign, long long n, int d, int k,
-                                                   float* __restrict__ sums, float* __restrict__ counts) {
-  extern __shared__ float part[];  // [k * d] sums, then [k] counts
+                                                   float* __restrict__ sums, unsigned int* __restrict__ counts) {
+  extern __shared__ float part[];  // [k * d] sums, then [k] counts (unsigned int, all-zero bits = 0 either way)
+  unsigned int* part_counts = reinterpret_cast<unsigned int*>(part + k * d);
   const int cells = k * d + k;
   for (int i = threadIdx.x; i < cells; i += blockDim.x) part[i] = 0.f;
   __syncthreads();
@@ -1558,24 +1572,31 @@ __global__ void fbmm_kmeans_accumulate_smem_kernel(const float* __restrict__ x, 
     const float* row = x + i * ldx;
     float* dst = part + c * d;
     for (int j = lane; j < d; j += 32) atomicAdd(dst + j, row[j]);
-    if (lane == 0) atomicAdd(part + k * d + c, 1.f);
+    if (lane == 0) atomicAdd(part_counts + c, 1u);
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < cells; i += blockDim.x) {
+  for (int i = threadIdx.x; i < k * d; i += blockDim.x) {
     const float v = part[i];
-    if (v != 0.f) atomicAdd(i < k * d ? sums + i : counts + (i - k * d), v);
+    if (v != 0.f) atomicAdd(sums + i, v);
+  }
+  for (int i = threadIdx.x; i < k; i += blockDim.x) {
+    const unsigned int c = part_counts[i];
+    if (c != 0u) atomicAdd(counts + i, c);
   }
 }
 
 // centroids[c][:] = sums[c][:] / counts[c]; a centroid no point chose keeps its old place.
-__global__ void fbmm_kmeans_finalize_kernel(const float* __restrict__ sums, const float* __restrict__ counts,
-                                            float* __restrict__ centroids, long long ldc, int d, long long total) {
+// counts_out (or null) receives the cluster sizes as fp32.
+__global__ void fbmm_kmeans_finalize_kernel(const float* __restrict__ sums, const unsigned int* __restrict__ counts,
+                                            float* __restrict__ centroids, long long ldc, int d, long long total,
+                                            float* __restrict__ counts_out) {
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= total) return;
   const long long c = i / d;
   const int j = static_cast<int>(i - c * d);
-  const float cnt = counts[c];
-  if (cnt > 0.f) centroids[c * ldc + j] = sums[i] / cnt;
+  const unsigned int cnt = counts[c];
+  if (cnt > 0u) centroids[c * ldc + j] = sums[i] / static_cast<float>(cnt);
+  if (j == 0 && counts_out != nullptr) counts_out[c] = static_cast<float>(cnt);
 }
 
 }  // namespace fbmm

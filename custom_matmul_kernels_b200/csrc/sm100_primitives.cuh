@@ -19,27 +19,11 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 
 __device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
 
-// One lane of a fully converged warp.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred = 0;
-  asm volatile(
-      "{\n"
-      ".reg .pred P;\n"
-      "elect.sync _|P, 0xffffffff;\n"
-      "selp.u32 %0, 1, 0, P;\n"
-      "}\n"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 // ----------------------------------------------------------------------------------
 // mbarrier
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_inval(uint64_t* bar) {
-  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)));
 }
 // Makes mbarrier initialisation visible to the async proxy (TMA, tcgen05.commit).
 __device__ __forceinline__ void fence_barrier_init() {
@@ -74,15 +58,16 @@ constexpr long long kWaitBudgetCycles = 4000000000LL;
 // thread of the CTA has given up, every other wait returns false at once so that the
 // whole CTA drains quickly. Returns true when the phase completed.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
+                                          volatile uint32_t* abort_flag,
+                                          long long budget_cycles = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 0x3ffu) == 0) {
+    if ((++spins & 0x3fu) == 0) {
       if (*abort_flag != 0) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget_cycles) {
         *abort_flag = 1;
         return false;
       }
@@ -175,19 +160,10 @@ __device__ __forceinline__ void tcgen05_fence_after_sync() {
 //   bits [46,48) descriptor version (1 on sm_100)
 //   bits [61,64) layout type (2 = 128-byte swizzle)
 // K-major tile (rows of 32 fp32 = 128 B, 8-row groups 1024 B apart): lbo is unused,
-// sbo = 1024. MN-major tile (rows of 32 consecutive M/N elements, one row per k, 8-k
-// groups 1024 B apart, 32-element column chunks `lbo` bytes apart): sbo = 1024.
-__device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                         uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  d |= static_cast<uint64_t>(2) << 61;
-  return d;
-}
-
+// sbo = 1024, layout type 2. MN-major tf32 tile (TMA SWIZZLE_128B_ATOM_32B): layout type 1,
+// lbo = distance between 32-element chunks, sbo = 512. The MMA issuer of the fused kernel
+// assembles these fields itself, as two 32-bit halves, because it has to issue one MMA
+// every 64 cycles.
 // Instruction descriptor for kind::tf32, fp32 accumulate, dense.
 //   bits [4,6) D format (1 = f32), [7,10) A format (2 = tf32), [10,13) B format,
 //   bit 15 A major (0 = K, 1 = MN), bit 16 B major, [17,23) N >> 3, [24,29) M >> 4.

@@ -24,6 +24,8 @@ FBMM_ERR_WORKSPACE = -3
 FBMM_ERR_CUDA = -4
 FBMM_ERR_DEVICE = -5
 FBMM_ERR_UNSUPPORTED = -6
+FBMM_ERR_PEER = -7
+FBMM_ERR_COMM = -8
 FBMM_DIST_INNER = 0
 FBMM_DIST_L2 = 1
 
@@ -60,12 +62,24 @@ SIGNATURES = {
                                                          _c_int, _c_ptr, _c_size]),
     "fbmm_min_bmm_f32_noalloc": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                                                                  _c_int]),
-    "fbmm_presplit_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int, _c_ll,
-                                                _c_ll]),
+    "fbmm_presplit_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_int,
+                                                _c_ll, _c_ll]),
     "fbmm_topk_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_topk_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                           _c_int, _c_int, _c_ll, _c_ptr, _c_size]),
     "fbmm_topk_merge_f32": (_c_int, [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_ptr, _c_ptr]),
+    "fbmm_topk_bmm_packed_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                                 _c_int, _c_ptr, _c_size]),
+    "fbmm_topk_merge_packed_f32": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_ll, _c_int, _c_ll, _c_ptr, _c_ptr]),
+    "fbmm_comm_get_unique_id": (_c_int, [_c_ptr]),
+    "fbmm_comm_init_rank": (_c_int, [ctypes.POINTER(_c_ptr), _c_int, _c_int, _c_ptr]),
+    "fbmm_comm_destroy": (_c_int, [_c_ptr]),
+    "fbmm_topk_bmm_sharded_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll,
+                                                        _c_int, _c_ll]),
+    "fbmm_topk_bmm_sharded_f32": (_c_int, [_c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_int, _c_ll, _c_ptr, _c_int, _c_ll,
+                                           _c_ll, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                                           _c_size]),
+    "fbmm_selftest_wait_expiry": (_c_int, [_c_ptr]),
     "fbmm_bmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ll, _c_ll, _c_int,
                               _c_int, _c_int, _c_int]),
     "fbmm_mbmm_x16": (_c_int, [_c_ptr, _c_ptr, _c_ll, _c_ll, _c_ptr, _c_ll, _c_ll, _c_int, _c_ptr, _c_ll, _c_ll, _c_ptr,
@@ -123,14 +137,16 @@ def operand(X: torch.Tensor):
     Returns (tensor_to_keep_alive, transposed, pitch, batch_stride): `transposed` is True
     when the storage runs along r (the reference's "t" stride layout, bmm.py:56-66).
     Storage the TMA engine cannot address (unaligned base, pitch or batch stride not a
-    multiple of 4 elements, neither of the last two strides equal to 1, broadcast batch)
-    is repacked into a row-major buffer whose pitch is rounded up to 4 elements."""
+    multiple of 4 elements, neither of the last two strides equal to 1) is repacked into a
+    row-major buffer whose pitch is rounded up to 4 elements. A batch stride of 0 (one matrix
+    expanded over the batch axis) is passed through as it is: the library reads the one
+    matrix for every batch."""
     l, r, c = X.shape
     sl, sr, sc = X.stride()
 
     def addressable(ld, inner):
         return (X.data_ptr() % 16 == 0 and ld % 4 == 0 and ld >= inner
-                and (l == 1 or (sl % 4 == 0 and sl > 0)))
+                and (l == 1 or (sl % 4 == 0 and sl >= 0)))
 
     if sc == 1 and addressable(sr, c):
         return X, False, sr, sl
@@ -179,6 +195,17 @@ class CustomKernel:
 
     def __init__(self):
         self.lib = load_library()
+
+    def get_mode(self, A, B):
+        """Stride layout of the last two dims of A and B, 'n' or 't' each, as the reference's
+        wrappers detect it (bmm.py:56-66); '?' where neither stride is 1."""
+        mode = [None, None]
+        for i, X in enumerate((A, B)):
+            if X.stride()[-1] == 1:
+                mode[i] = "n"
+            elif X.stride()[-2] == 1:
+                mode[i] = "t"
+        return "".join(m or "?" for m in mode)
 
     @staticmethod
     def stream_ptr(device: torch.device) -> int:

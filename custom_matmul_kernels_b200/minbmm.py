@@ -27,15 +27,6 @@ class MinBMMCUDA(CustomKernel):
         self._distance_code = distance_code(distance)
         self.distance = distance
 
-    def get_mode(self, A, B):
-        mode = [None, None]
-        for i, X in enumerate((A, B)):
-            if X.stride()[-1] == 1:
-                mode[i] = "n"
-            elif X.stride()[-2] == 1:
-                mode[i] = "t"
-        return "".join(m or "?" for m in mode)
-
     def __call__(self, A, B, dim=1):
         A3, B3, two_d = self.check_inputs(A, B, (torch.float32,) + _X16)
         if two_d:
@@ -65,7 +56,7 @@ class MinBMMCUDA(CustomKernel):
         b_keep, b_t, ldb, sb = operand(B3)
         # own scratch (packed keys) plus, for large problems, room for pre-split lo planes
         ws_bytes = (self.lib.fbmm_min_bmm_workspace_bytes(l, m, n, k, dim, self._distance_code) + 255) // 256 * 256
-        ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, k, layout_letter(a_t, False), lda, sa,
+        ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, k, dim, layout_letter(a_t, False), lda, sa,
                                                            layout_letter(b_t, True), ldb, sb)
         ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
         with torch.cuda.device(A3.device):

@@ -7,8 +7,10 @@ reference behaviour to match beyond "same answer as one device". Three partition
 * by A rows       min / top-k with one batch: each rank owns M/G rows and the whole B, no
                   communication;
 * by B columns    top-k against a very wide B: each rank owns N/G columns and the whole A,
-                  produces its local top-k with GLOBAL column indices, then ONE all-gather
-                  of the (value, index) candidates and a merge kernel on every rank.
+                  writes its local top-k as packed 8-byte candidates {fp32 value, int32
+                  shard-local column} straight into the send buffer, then ONE all-gather and a
+                  merge kernel on every rank that adds each shard's first column and widens
+                  the indices to int64.
 
 The compute callables are injected so that the partition / exchange logic can be tested
 with CPU tensors over the gloo backend.
@@ -21,16 +23,25 @@ import torch
 import torch.distributed as dist
 
 
+class PeerFailure(RuntimeError):
+    """Another rank failed in its local step; this rank skipped the exchange and the merge."""
+
+
 def shard_range(total: int, world: int, rank: int, granule: int = 1) -> Tuple[int, int]:
     """[begin, end) of `rank`'s contiguous share of `total` items, split in multiples of
     `granule` (the last ranks may get less, or nothing)."""
     if world <= 0 or not 0 <= rank < world:
         raise ValueError(f"bad rank {rank} / world {world}")
-    blocks = (total + granule - 1) // granule
-    per = (blocks + world - 1) // world
-    b = min(total, rank * per * granule)
-    e = min(total, (rank + 1) * per * granule)
+    stride = shard_stride(total, world, granule)
+    b = min(total, rank * stride)
+    e = min(total, (rank + 1) * stride)
     return b, e
+
+
+def shard_stride(total: int, world: int, granule: int = 1) -> int:
+    """Items between the first items of consecutive ranks' shares (see shard_range)."""
+    blocks = (total + granule - 1) // granule
+    return (blocks + world - 1) // world * granule
 
 
 def world_info(group=None) -> Tuple[int, int]:
@@ -60,6 +71,21 @@ def column_shard(B: torch.Tensor, group=None) -> Tuple[torch.Tensor, int]:
     return B[:, :, b:e], b
 
 
+# ---------------------------------------------------------------------------------------
+# wire format of the candidate exchange: one int64 per entry, low half = fp32 value bits,
+# high half = int32 shard-local column (-1 = empty slot). In memory (little endian) that is
+# { float value; int index; }, what fbmm_topk_bmm_packed_f32 writes.
+# ---------------------------------------------------------------------------------------
+def pack_candidates(values: torch.Tensor, local_indices: torch.Tensor) -> torch.Tensor:
+    bits = values.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    return (local_indices.to(torch.int64) << 32) | bits
+
+
+def unpack_candidates(packed: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    low_halves = packed.contiguous().view(torch.int32)[..., 0::2]  # little endian: the value comes first
+    return low_halves.contiguous().view(torch.float32), packed >> 32
+
+
 def merge_candidates_torch(cand_v: torch.Tensor, cand_i: torch.Tensor, k: int):
     """Reference merge of [groups, rows, k] candidate lists with torch ops (CPU tests)."""
     g, rows, kk = cand_v.shape
@@ -68,6 +94,13 @@ def merge_candidates_torch(cand_v: torch.Tensor, cand_i: torch.Tensor, k: int):
     v = torch.where(i < 0, torch.full_like(v, float("-inf")), v)
     top_v, sel = v.topk(k, dim=-1)
     return top_v, torch.gather(i, 1, sel)
+
+
+def merge_packed_torch(packed: torch.Tensor, k: int, group_index_stride: int):
+    """Torch statement of fbmm_topk_merge_packed_f32 for [groups, rows, k] packed lists (CPU tests)."""
+    v, i = unpack_candidates(packed)
+    offs = (torch.arange(packed.shape[0], device=packed.device, dtype=torch.int64) * group_index_stride)[:, None, None]
+    return merge_candidates_torch(v, torch.where(i >= 0, i + offs, i), k)
 
 
 def merge_candidates_cuda(cand_v: torch.Tensor, cand_i: torch.Tensor, k: int):
@@ -84,27 +117,72 @@ def merge_candidates_cuda(cand_v: torch.Tensor, cand_i: torch.Tensor, k: int):
     return out_v, out_i
 
 
-def topk_bmm_column_sharded(A: torch.Tensor, B_local: torch.Tensor, col_offset: int, k: int,
-                            local_topk: Callable, merge: Callable = merge_candidates_cuda, group=None):
-    """Top-k of A @ [B_0 | B_1 | ...] where this rank holds B_local (columns starting at
-    `col_offset`) and all of A [1, m, d].
+def merge_packed_cuda(packed: torch.Tensor, k: int, group_index_stride: int):
+    """[groups, rows, k] packed candidates -> ([rows, k] fp32, [rows, k] int64 global indices)
+    through fbmm_topk_merge_packed_f32, read in place from the gathered buffer."""
+    from .custom_kernel import check, load_library
+    lib = load_library()
+    g, rows, kk = packed.shape
+    assert kk == k and packed.is_contiguous() and packed.dtype == torch.int64
+    out_v = torch.empty((rows, k), device=packed.device, dtype=torch.float32)
+    out_i = torch.empty((rows, k), device=packed.device, dtype=torch.int64)
+    with torch.cuda.device(packed.device):
+        check(lib.fbmm_topk_merge_packed_f32(torch.cuda.current_stream(packed.device).cuda_stream, packed.data_ptr(), g,
+                                             rows, k, group_index_stride, out_v.data_ptr(), out_i.data_ptr()))
+    return out_v, out_i
 
-    local_topk(A, B_local, k, index_offset) -> (values [1,m,k], indices [1,m,k]) with
-    global column indices; ranks whose shard is empty contribute -inf / -1. The
-    candidates are exchanged with ONE all_gather per tensor and merged on every rank.
-    Returns (values [1,m,k], indices [1,m,k])."""
+
+def topk_bmm_column_sharded(A: torch.Tensor, B_local: torch.Tensor, cols_per_rank: int, k: int,
+                            local_packed: Callable, merge: Callable = merge_packed_cuda, group=None,
+                            check_peers: bool = True, timings: dict | None = None):
+    """Top-k of A @ [B_0 | B_1 | ...] where this rank holds B_local, the columns
+    [rank * cols_per_rank, ...) of B, and all of A [1, m, d].
+
+    local_packed(A, B_local, k) -> int64 [1, m, k] packed candidates with shard-local
+    columns (TopkBMMCUDA.packed); a rank whose shard is empty contributes empty slots. The
+    candidates are exchanged with ONE all_gather and merged on every rank by
+    merge(gathered [world, m, k], k, cols_per_rank). Returns (values [1,m,k], indices [1,m,k]).
+
+    With check_peers the ranks first agree, through a 4-byte all-reduce, that every local
+    step succeeded: if one raised, that rank re-raises, the others raise PeerFailure, and
+    nobody enters the all-gather or runs the merge. `timings` (CUDA only), when given,
+    receives the events around the three phases."""
     rank, world = world_info(group)
     m = A.shape[1]
-    if B_local.shape[2] > 0:
-        v, i = local_topk(A, B_local, k, col_offset)
-    else:
-        v = torch.full((1, m, k), float("-inf"), device=A.device, dtype=torch.float32)
-        i = torch.full((1, m, k), -1, device=A.device, dtype=torch.int64)
+    cuda = A.device.type == "cuda"
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if (timings is not None and cuda) else None
+    if ev:
+        ev[0].record()
+    err = None
+    packed = None
+    try:
+        if B_local.shape[2] > 0:
+            packed = local_packed(A, B_local, k).reshape(m, k)
+        else:
+            packed = pack_candidates(torch.full((m, k), float("-inf"), device=A.device),
+                                     torch.full((m, k), -1, device=A.device, dtype=torch.int64))
+    except Exception as e:  # noqa: BLE001 -- reported to the peers below, then re-raised
+        err = e
+    if ev:
+        ev[1].record()
+    if world > 1 and check_peers:
+        flag = torch.tensor([0 if err is None else 1], device=A.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+        if int(flag.item()) != 0:
+            if err is not None:
+                raise err
+            raise PeerFailure("another rank failed in its local top-k; the exchange and the merge were skipped")
+    elif err is not None:
+        raise err
     if world == 1:
-        return v, i
-    all_v = torch.empty((world, m, k), device=A.device, dtype=torch.float32)
-    all_i = torch.empty((world, m, k), device=A.device, dtype=torch.int64)
-    dist.all_gather_into_tensor(all_v, v.reshape(1, m, k).contiguous(), group=group)
-    dist.all_gather_into_tensor(all_i, i.reshape(1, m, k).contiguous(), group=group)
-    mv, mi = merge(all_v, all_i, k)
+        gathered = packed.reshape(1, m, k)
+    else:
+        gathered = torch.empty((world, m, k), device=A.device, dtype=torch.int64)
+        dist.all_gather_into_tensor(gathered, packed.reshape(1, m, k).contiguous(), group=group)
+    if ev:
+        ev[2].record()
+    mv, mi = merge(gathered, k, cols_per_rank)
+    if ev:
+        ev[3].record()
+        timings["events"] = ev
     return mv[None], mi[None]

@@ -28,15 +28,6 @@ class TopkBMMCUDA(CustomKernel):
         self._distance_code = distance_code(distance)
         self.distance = distance
 
-    def get_mode(self, A, B):
-        mode = [None, None]
-        for i, X in enumerate((A, B)):
-            if X.stride()[-1] == 1:
-                mode[i] = "n"
-            elif X.stride()[-2] == 1:
-                mode[i] = "t"
-        return "".join(m or "?" for m in mode)
-
     def __call__(self, A, B, k=128, dim=1, index_offset=0):
         A3, B3, two_d = self.check_inputs(A, B, (torch.float32,) + _X16)
         if two_d:
@@ -70,7 +61,7 @@ class TopkBMMCUDA(CustomKernel):
         with torch.cuda.device(A3.device):
             # own scratch (per-chunk lists) plus, for large problems, room for pre-split lo planes
             ws_bytes = (self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim, self._distance_code) + 255) // 256 * 256
-            ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, d, layout_letter(a_t, False), lda, sa,
+            ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, d, dim, layout_letter(a_t, False), lda, sa,
                                                                layout_letter(b_t, True), ldb, sb)
             ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
             check(self.lib.fbmm_topk_bmm_f32(
@@ -82,3 +73,37 @@ class TopkBMMCUDA(CustomKernel):
         if two_d:
             return values[0], indices[0]
         return values, indices
+
+    def packed(self, A, B, k=128, dim=1):
+        """The same top-k in wire format: one int64 per entry whose low half holds the fp32
+        value's bits and whose high half holds the int32 index (-1 = empty), indices being
+        plain positions along `dim` of THIS call's operands. A rank that owns a column shard
+        of B hands this tensor to one all-gather as it is (sharding.topk_bmm_column_sharded);
+        sharding.unpack_candidates splits it again. fp32 operands only. Shape [l, rows, k]
+        ([rows, k] for 2-D inputs)."""
+        A3, B3, two_d = self.check_inputs(A, B, (torch.float32,))
+        if two_d:
+            dim += 1
+        if dim not in (1, 2):
+            raise ValueError("dim must be 1 or 2 on the 3-D product (0 or 1 for 2-D inputs)")
+        if not 0 < k <= 128:
+            raise ValueError("k must be in 1..128")
+        l, m, d = A3.shape
+        n = B3.shape[2]
+        if min(l, m, n, d) <= 0:
+            raise ValueError(f"empty problem: l={l} m={m} n={n} k={d}")
+        rows = n if dim == 1 else m
+        out = torch.empty((l, rows, k), device=A3.device, dtype=torch.int64)
+        a_keep, a_t, lda, sa = operand(A3)
+        b_keep, b_t, ldb, sb = operand(B3)
+        with torch.cuda.device(A3.device):
+            ws_bytes = (self.lib.fbmm_topk_bmm_workspace_bytes(l, m, n, d, k, dim, self._distance_code) + 255) // 256 * 256
+            ws_bytes += self.lib.fbmm_presplit_workspace_bytes(l, m, n, d, dim, layout_letter(a_t, False), lda, sa,
+                                                               layout_letter(b_t, True), ldb, sb)
+            ws = torch.empty(max(ws_bytes, 256), device=A3.device, dtype=torch.uint8)
+            check(self.lib.fbmm_topk_bmm_packed_f32(
+                self.stream_ptr(A3.device),
+                a_keep.data_ptr(), layout_letter(a_t, False), lda, sa,
+                b_keep.data_ptr(), layout_letter(b_t, True), ldb, sb,
+                out.data_ptr(), l, m, n, d, k, dim, self._distance_code, ws.data_ptr(), ws_bytes))
+        return out[0] if two_d else out

@@ -16,7 +16,11 @@
  *    `stride_*` the distance, in elements, between consecutive batches.
  *  - TMA requirements: operand base pointers 16-byte aligned, pitches and batch strides
  *    multiples of 4 elements. Violations return FBMM_ERR_ALIGN (the Python wrappers
- *    repack such operands before calling).
+ *    repack such operands before calling). A batch stride of 0 with l > 1 means one matrix
+ *    shared by every batch (a broadcast operand).
+ *  - Non-finite values: a NaN product never wins a min (a row whose products are all NaN
+ *    returns +inf and index 0) and is never listed by top-k, which also never lists -inf
+ *    (such rows are padded with -inf / -1 like rows with fewer than topk entries).
  *  - The library allocates no memory. Scratch comes from the caller through
  *    `workspace` / `workspace_bytes`, sized by the matching *_workspace_bytes query.
  *  - Return value: FBMM_OK or a negative FBMM_ERR_* code; fbmm_last_error() gives the
@@ -38,6 +42,8 @@ extern "C" {
 #define FBMM_ERR_CUDA (-4)        /* a CUDA runtime / driver call failed */
 #define FBMM_ERR_DEVICE (-5)      /* a kernel reported a bounded wait that ran out */
 #define FBMM_ERR_UNSUPPORTED (-6) /* not an sm_100 device */
+#define FBMM_ERR_PEER (-7)        /* sharded call: another rank reported a failure */
+#define FBMM_ERR_COMM (-8)        /* NCCL could not be loaded or one of its calls failed */
 
 /* `distance` of min_bmm / topk_bmm, the reference's accumulate functions
  * (minbmm.py:12-19, kernels/bmm_helpers.cu:20-35): inner product (madd) or squared
@@ -105,10 +111,11 @@ int fbmm_min_bmm_f32(void* stream,
 /* min_bmm for callers that cannot allocate device memory and cannot supply scratch: a
  * serving loop with a memory budget frozen at start-up, or a plugin host that passes an
  * operator only its inputs and outputs (no torch allocator, and a cudaMalloc at call time
- * would synchronise the device or fail). Same arguments and results as fbmm_min_bmm_f32
- * minus the workspace; the 8-byte-per-row key scratch lives in a 2 MiB device array inside
- * the library (held by every GPU that loads it, until exit). It has no counterpart in the
- * reference.
+ * would synchronise the device or fail). Arguments and results as fbmm_min_bmm_f32 without
+ * the workspace and without `distance`: this entry point reduces the inner product only
+ * (there is no FBMM_DIST_L2 path here, because the norms would need scratch too). The
+ * 8-byte-per-row key scratch lives in a 2 MiB device array inside the library (held by
+ * every GPU that loads it, until exit). It has no counterpart in the reference.
  *  - Limit: l * (m for dim 2, n for dim 1) <= 262144 output rows per call; more returns
  *    FBMM_ERR_WORKSPACE with a message naming the limit.
  *  - Calls no cudaMalloc / cudaFree or allocating library routine. The first call on a
@@ -132,9 +139,11 @@ int fbmm_min_bmm_f32_noalloc(void* stream,
  * A column operand of 64 MB or more that is stored with n contiguous gets both its planes
  * written there k-contiguous (so this query can exceed the operands' own size). Returns 0
  * for shapes where it would not be used (fewer than 1024 rows or columns, or storage with
- * large gaps). Same answers either way. No reference counterpart (its kernels multiply in
- * fp32 on the CUDA cores, kernels/bmm_helpers.cu:20-26). */
-size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k,
+ * large gaps). `dim` is the dim of the call the scratch is for: with dim = 1 the operands
+ * swap roles (B supplies the rows), and so do their planes. Same answers either way. No
+ * reference counterpart (its kernels multiply in fp32 on the CUDA cores,
+ * kernels/bmm_helpers.cu:20-26). */
+size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k, int dim,
                                      int a_layout, long long lda, long long stride_a,
                                      int b_layout, long long ldb, long long stride_b);
 
@@ -166,6 +175,58 @@ int fbmm_topk_merge_f32(void* stream,
                         const float* cand_values, const long long* cand_indices,
                         int groups, long long rows, int topk,
                         float* out_values, long long* out_indices);
+
+/* topk_bmm with the result in wire format: `candidates` receives [l, rows, topk] entries of
+ * 8 bytes, { float value; int index; }, descending, empty entries (-inf, -1). Indices are
+ * plain column (dim = 2) or row (dim = 1) numbers of THIS call's operands, so a rank that
+ * holds a column shard of B can hand the buffer to one all-gather as it is. Workspace as
+ * fbmm_topk_bmm_f32 (same query). No reference counterpart: the reference is single-GPU
+ * (outputs hard-wired to cuda:0, topkbmm.py:120-126). */
+int fbmm_topk_bmm_packed_f32(void* stream,
+                             const float* A, int a_layout, long long lda, long long stride_a,
+                             const float* B, int b_layout, long long ldb, long long stride_b,
+                             void* candidates,
+                             int l, int m, int n, int k, int topk, int dim, int distance,
+                             void* workspace, size_t workspace_bytes);
+
+/* Merge of `groups` packed candidate lists per row, laid out [groups][rows][topk] as an
+ * all-gather of fbmm_topk_bmm_packed_f32 results leaves them; group g's indices get
+ * g * group_index_stride added (the first column of shard g) and come out as int64. The
+ * packed form of fbmm_topk_merge_f32 (kernels/bitonic_sort.cu:183-216 analogue). */
+int fbmm_topk_merge_packed_f32(void* stream, const void* candidates, int groups, long long rows, int topk,
+                               long long group_index_stride, float* out_values, long long* out_indices);
+
+/* Column-sharded top-k for hosts that are not Python: rank `rank` of `world` holds all of A
+ * [m, k] and the columns [rank * cols_per_rank, rank * cols_per_rank + n_local) of B as
+ * B_local (n_local may be 0 on trailing ranks). Every rank computes its local top-k in wire
+ * format into the workspace, ONE ncclAllGather exchanges the lists, and every rank merges
+ * them: values / indices [m, topk] hold the global result, indices global column numbers.
+ * `comm` is an ncclComm_t (as void*), either the host's own or one made by
+ * fbmm_comm_init_rank; NCCL is loaded with dlopen("libnccl.so.2") (FBMM_NCCL_LIB overrides
+ * the name), which resolves to the copy the process already holds if there is one.
+ * With check_peers != 0 the ranks first agree (one 4-byte all-reduce and a stream
+ * synchronisation) that every local step was enqueued; if one failed, that rank returns its
+ * own error, the others FBMM_ERR_PEER, and nobody enters the all-gather. With 0 the call
+ * stays asynchronous and a rank that fails locally leaves its peers waiting in the
+ * collective until the host aborts the communicator. The reference has no multi-GPU path. */
+int fbmm_comm_get_unique_id(void* id128);                                   /* rank 0: 128 bytes to hand to every rank */
+int fbmm_comm_init_rank(void** comm, int world, int rank, const void* id128); /* collective over all ranks */
+int fbmm_comm_destroy(void* comm);
+size_t fbmm_topk_bmm_sharded_workspace_bytes(int world, int m, int n_local, int k, int topk, int distance,
+                                             int a_layout, long long lda, int b_layout, long long ldb);
+int fbmm_topk_bmm_sharded_f32(void* stream, void* comm, int world, int rank,
+                              const float* A, int a_layout, long long lda,
+                              const float* B_local, int b_layout, long long ldb, long long cols_per_rank,
+                              float* values, long long* indices,
+                              int m, int n_local, int k, int topk, int distance, int check_peers,
+                              void* workspace, size_t workspace_bytes);
+
+/* Exercises the bounded-wait path on purpose, harmlessly: a one-warp kernel waits ~2e5 cycles
+ * on a barrier nobody arrives on, gives up, and leaves through the same status word the fused
+ * kernels use, so the next fbmm_check() on that stream returns FBMM_ERR_DEVICE once and
+ * FBMM_OK after. No reference counterpart (its spin mutex gives up silently,
+ * kernels/topkbmm.cu:23). */
+int fbmm_selftest_wait_expiry(void* stream);
 
 /* bmm, mbmm, min_bmm and topk_bmm on fp16 / bf16 operands (dtype FBMM_F16 / FBMM_BF16); C of
  * bmm / mbmm has the operands' type (as the reference allocates it, bmm.py:106),

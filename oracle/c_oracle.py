@@ -23,6 +23,9 @@ def _lib():
     return ctypes.CDLL(build())
 
 
+_DIST = {"inner": 0, "l2": 1, "euclidean": 1, "l1": 2, "manhattan": 2}
+
+
 def _f(t):
     return np.ascontiguousarray(t.detach().cpu().numpy(), dtype=np.float32)
 
@@ -57,7 +60,7 @@ def min_bmm(A, B, dim, distance="inner"):
     r = m if dim == 2 else n
     v = np.empty((l, r), np.float32)
     i = np.empty((l, r), np.int64)
-    _lib().oracle_min_bmm(_p(a), _p(b), _p(v), _p(i), l, m, n, k, dim, int(distance != "inner"))
+    _lib().oracle_min_bmm(_p(a), _p(b), _p(v), _p(i), l, m, n, k, dim, _DIST[distance])
     return torch.from_numpy(v), torch.from_numpy(i)
 
 
@@ -68,5 +71,5 @@ def topk_bmm(A, B, topk, dim, distance="inner"):
     r = m if dim == 2 else n
     v = np.empty((l, r, topk), np.float32)
     i = np.empty((l, r, topk), np.int64)
-    _lib().oracle_topk_bmm(_p(a), _p(b), _p(v), _p(i), l, m, n, k, topk, dim, int(distance != "inner"))
+    _lib().oracle_topk_bmm(_p(a), _p(b), _p(v), _p(i), l, m, n, k, topk, dim, _DIST[distance])
     return torch.from_numpy(v), torch.from_numpy(i)

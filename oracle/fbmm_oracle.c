@@ -13,9 +13,13 @@
  *   - mbmm zeroes a 128x128 tile whose block-mask byte is 0 (kernels/mbmm.cu:251-255),
  *     an 8x8 tile whose thread-mask byte is 0 (:360-363), and multiplies the rest by the
  *     element-mask byte (:111-133).
- * Parity status: no golden vectors exist in the reference, so this restatement is pinned
- * only against the torch test expressions (tests/test_oracle.py) -- index choice between
- * equal values is unpinned in the reference itself.
+ * Parity status: the reference ships no golden vectors, so this restatement is pinned (a) to
+ * the reference's torch test expressions (tests/test_oracle.py) and (b) to outputs of the
+ * reference's own kernels, compiled from its sources by oracle/build_ref.py and run on a GPU
+ * (tests/test_gpu_reference_kernels.py): bmm and mbmm outputs and min values must match this
+ * file bit for bit. top-k is pinned by (a) only (the reference's top-k kernel takes a global
+ * spin mutex and is not run); index choice between equal values is unpinned in the reference
+ * itself (its value / index update is racy, kernels/minbmm.cu:76-79).
  *
  * Matrices are dense row-major: A[l][m][k], B[l][k][n].
  */
@@ -40,8 +44,16 @@ static float dist_l2(const float* a, const float* b, int K, long long ldb) {
   return acc;
 }
 
-static float entry(const float* a, const float* b, int K, long long ldb, int l2) {
-  return l2 ? dist_l2(a, b, K, ldb) : dot_fma(a, b, K, ldb);
+/* l1 (kernels/bmm_helpers.cu:46-52): c += fabsf(a - b). */
+static float dist_l1(const float* a, const float* b, int K, long long ldb) {
+  float acc = 0.0f;
+  for (int k = 0; k < K; ++k) acc += fabsf(a[k] - b[(long long)k * ldb]);
+  return acc;
+}
+
+/* dist: 0 = inner product (madd), 1 = squared_l2, 2 = l1 (minbmm.py:12-19). */
+static float entry(const float* a, const float* b, int K, long long ldb, int dist) {
+  return dist == 1 ? dist_l2(a, b, K, ldb) : (dist == 2 ? dist_l1(a, b, K, ldb) : dot_fma(a, b, K, ldb));
 }
 
 void oracle_bmm(const float* A, const float* B, float* C, int L, int M, int N, int K) {
@@ -73,7 +85,7 @@ void oracle_mbmm(const float* A, const float* B, float* C, const uint8_t* block_
 
 /* dim == 2: one result per row m (min over n); dim == 1: one result per column n. */
 void oracle_min_bmm(const float* A, const float* B, float* values, long long* indices, int L, int M, int N, int K,
-                    int dim, int l2) {
+                    int dim, int dist) {
   for (int l = 0; l < L; ++l) {
     const int R = dim == 2 ? M : N, S = dim == 2 ? N : M;
     for (int r = 0; r < R; ++r) {
@@ -81,7 +93,7 @@ void oracle_min_bmm(const float* A, const float* B, float* values, long long* in
       long long best_i = 0;
       for (int s = 0; s < S; ++s) {
         const int m = dim == 2 ? r : s, n = dim == 2 ? s : r;
-        const float c = entry(A + ((long long)l * M + m) * K, B + (long long)l * K * N + n, K, N, l2);
+        const float c = entry(A + ((long long)l * M + m) * K, B + (long long)l * K * N + n, K, N, dist);
         if (c < best) { best = c; best_i = s; }
       }
       values[(long long)l * R + r] = best;
@@ -92,7 +104,7 @@ void oracle_min_bmm(const float* A, const float* B, float* values, long long* in
 
 /* Output [l][R][topk], descending; ties keep the lower index first. */
 void oracle_topk_bmm(const float* A, const float* B, float* values, long long* indices, int L, int M, int N, int K,
-                     int topk, int dim, int l2) {
+                     int topk, int dim, int dist) {
   for (int l = 0; l < L; ++l) {
     const int R = dim == 2 ? M : N, S = dim == 2 ? N : M;
     for (int r = 0; r < R; ++r) {
@@ -101,7 +113,7 @@ void oracle_topk_bmm(const float* A, const float* B, float* values, long long* i
       int cnt = 0;
       for (int s = 0; s < S; ++s) {
         const int m = dim == 2 ? r : s, n = dim == 2 ? s : r;
-        const float c = entry(A + ((long long)l * M + m) * K, B + (long long)l * K * N + n, K, N, l2);
+        const float c = entry(A + ((long long)l * M + m) * K, B + (long long)l * K * N + n, K, N, dist);
         int pos = cnt;
         while (pos > 0 && v[pos - 1] < c) --pos;      /* strict: earlier index stays ahead on ties */
         if (pos >= topk) continue;

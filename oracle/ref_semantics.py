@@ -128,6 +128,13 @@ def product(A3, B3, distance="inner", dtype=torch.float32):
             d = A3[:, r0:r0 + step, None, :] - Bt[:, None, :, :]
             out[:, r0:r0 + step] = (d * d).sum(-1)
         return out
+    if distance in ("l1", "manhattan"):  # l1, kernels/bmm_helpers.cu:46-52 (minbmm.py:16-17)
+        out = torch.empty(A3.shape[0], A3.shape[1], B3.shape[2], dtype=dtype)
+        step = max(1, (1 << 24) // max(1, A3.shape[2] * B3.shape[2]))
+        Bt = B3.transpose(1, 2)
+        for r0 in range(0, A3.shape[1], step):
+            out[:, r0:r0 + step] = (A3[:, r0:r0 + step, None, :] - Bt[:, None, :, :]).abs().sum(-1)
+        return out
     raise ValueError(f"distance {distance!r} is not restated")
 
 

@@ -87,6 +87,40 @@ def test_workspace_queries(lib):
     assert lib.fbmm_topk_bmm_workspace_bytes(1, 128, 1 << 16, 64, 64, 2, 0) > w64
 
 
+def test_presplit_query_follows_dim(lib):
+    """dim = 1 swaps the operands' roles; its scratch is that of the dim = 2 call on (B^T, A^T)."""
+    l, m, n, k = 1, 4096, 65536, 256
+    # A [m,k] row-major ('n'), B [k,n] row-major ('n'): as row problem of dim 1, rows come from B
+    # (stored [k][n], i.e. the 't' layout of a row operand) and columns from A (stored [m][k], the 't'
+    # layout of a column operand)
+    q1 = lib.fbmm_presplit_workspace_bytes(l, m, n, k, 1, ord("n"), k, m * k, ord("n"), n, k * n)
+    q2 = lib.fbmm_presplit_workspace_bytes(l, n, m, k, 2, ord("t"), n, k * n, ord("t"), k, m * k)
+    assert q1 == q2 > 0
+    assert q1 != lib.fbmm_presplit_workspace_bytes(l, m, n, k, 2, ord("n"), k, m * k, ord("n"), n, k * n)
+    assert lib.fbmm_presplit_workspace_bytes(l, m, n, k, 3, ord("n"), k, m * k, ord("n"), n, k * n) == 0
+
+
+def test_sharded_and_packed_validation(lib):
+    rc = lib.fbmm_topk_bmm_packed_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, None, 1, 4, 4, 4, 8, 2, 0, None, 0)
+    assert rc == ck.FBMM_ERR_INVALID and b"candidates" in lib.fbmm_last_error()
+    rc = lib.fbmm_topk_bmm_packed_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 68, 1, 4, 4, 4, 8, 2, 0, None, 0)
+    assert rc == ck.FBMM_ERR_ALIGN
+    rc = lib.fbmm_topk_merge_packed_f32(None, 64, 0, 4, 8, 128, 64, 64)
+    assert rc == ck.FBMM_ERR_INVALID
+    rc = lib.fbmm_topk_merge_packed_f32(None, 64, 2, 4, 8, -1, 64, 64)
+    assert rc == ck.FBMM_ERR_INVALID
+    # rank out of range, null communicator, missing workspace: all before any CUDA or NCCL call
+    args = lambda comm, world, rank, ws, wsb: lib.fbmm_topk_bmm_sharded_f32(  # noqa: E731
+        None, comm, world, rank, 64, ord("n"), 4, 64, ord("n"), 4, 4, 64, 64, 4, 4, 4, 2, 0, 1, ws, wsb)
+    assert args(1, 2, 2, None, 0) == ck.FBMM_ERR_INVALID
+    assert args(None, 2, 0, None, 0) == ck.FBMM_ERR_INVALID
+    assert args(1, 2, 0, None, 0) == ck.FBMM_ERR_WORKSPACE
+    need = lib.fbmm_topk_bmm_sharded_workspace_bytes(8, 1 << 20, 1 << 17, 256, 64, 0, ord("n"), 256, ord("n"), 1 << 17)
+    # send + 8 received lists of 2^20 x 64 entries of 8 bytes, plus the local step's scratch
+    assert need > 9 * (1 << 20) * 64 * 8
+    assert lib.fbmm_comm_init_rank(None, 2, 0, None) == ck.FBMM_ERR_INVALID
+
+
 def test_wrappers_reject_bad_inputs_on_cpu():
     from custom_matmul_kernels_b200 import BMMCUDA, MBMMCUDA, MinBMMCUDA, TopkBMMCUDA
     A, B = torch.zeros(2, 4, 8), torch.zeros(2, 8, 4)
@@ -137,9 +171,9 @@ def test_operand_descriptor_logic():
     off = torch.zeros(2 * 8 * 12 + 1)[1:].view(2, 8, 12)               # base off by 4 bytes
     keep, _, _, _ = ck.operand(off)
     assert keep.data_ptr() % 16 == 0
-    bc = torch.zeros(1, 8, 12).expand(3, 8, 12)                        # broadcast batch
+    bc = torch.zeros(1, 8, 12).expand(3, 8, 12)                        # broadcast batch: passed through
     keep, _, _, bs = ck.operand(bc)
-    assert bs == 96
+    assert keep is bc and bs == 0
 
 
 def test_make_masks_matches_oracle():

@@ -372,7 +372,7 @@ def test_presplit_scratch_gives_identical_bits(dev, lib):
     for (m, k, n) in [(1100, 96, 1300), (1024, 160, 1536), (1280, 128, 1100)]:
         A = torch.randn(1, m, k, generator=g).to(dev)
         B = torch.randn(1, k, n, generator=g).to(dev)
-        extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, ord("n"), k, m * k, ord("n"), n, k * n)
+        extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, 2, ord("n"), k, m * k, ord("n"), n, k * n)
         assert extra >= k * n * 4
         outs = []
         for use_extra in (False, True):
@@ -398,7 +398,7 @@ def test_presplit_scratch_gives_identical_bits(dev, lib):
             assert torch.equal(a, b)
         R.check_min(outs[1][0], outs[1][1], A.cpu(), B.cpu(), 2)
         R.check_topk(outs[1][2], outs[1][3], A.cpu(), B.cpu(), 16, 2)
-    assert lib.fbmm_presplit_workspace_bytes(1, 512, 4096, 64, ord("n"), 64, 0, ord("n"), 4096, 0) == 0
+    assert lib.fbmm_presplit_workspace_bytes(1, 512, 4096, 64, 2, ord("n"), 64, 0, ord("n"), 4096, 0) == 0
     assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
 
 
@@ -412,7 +412,7 @@ def test_topk_and_min_with_pre_split_planes_wider_than_l2(dev, lib):
     A = torch.randn(1, m, k, generator=g).to(dev)
     B = torch.randn(1, k, n, generator=g).to(dev)
     stream = torch.cuda.current_stream().cuda_stream
-    extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, ord("n"), k, m * k, ord("n"), n, k * n)
+    extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, 2, ord("n"), k, m * k, ord("n"), n, k * n)
     assert extra >= k * n * 4
     outs = []
     for use_extra in (False, True):
@@ -454,7 +454,7 @@ def test_topk_and_min_on_a_repacked_column_operand(ops, dev, lib):
     B = Bc.to(dev)
     Bt = B.transpose(1, 2).contiguous().transpose(1, 2)  # same values, stored [n][k]
     tk, mn = ops["topk"], ops["min"]
-    extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, ord("n"), k, m * k, ord("n"), n, k * n)
+    extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, 2, ord("n"), k, m * k, ord("n"), n, k * n)
     assert extra >= 2 * n * k * 4  # both planes of B
     tv, ti = tk(A, B, k=32, dim=2)
     tv2, ti2 = tk(A, Bt, k=32, dim=2)

@@ -32,6 +32,20 @@ def test_merge_candidates_torch_handles_empty_slots():
     assert mv.tolist() == [[5., 4., 4.]] and sorted(mi[0].tolist()) == [7, 9, 11]
 
 
+def test_pack_unpack_candidates_round_trip():
+    v = torch.tensor([[1.5, -2.0, float("-inf")], [0.0, -0.0, 3.25]])
+    i = torch.tensor([[7, 123456, -1], [0, 2147483646, 5]])
+    p = S.pack_candidates(v, i)
+    assert p.dtype == torch.int64
+    vv, ii = S.unpack_candidates(p)
+    assert torch.equal(vv.view(torch.int32), v.view(torch.int32)) and torch.equal(ii, i)
+    # in memory an entry is { float value; int index; }
+    raw = p.numpy().view("<i4").reshape(2, 3, 2)
+    assert raw[0, 1, 1] == 123456 and raw[0, 2, 1] == -1
+    mv, mi = S.merge_packed_torch(torch.stack([p, p]), 2, 1000)
+    assert mv[0].tolist() == [1.5, 1.5] and sorted(mi[0].tolist()) == [7, 1007]
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -48,16 +62,42 @@ def _worker(rank, world, port, out):
         B = torch.randn(1, 24, 1000, generator=g)
         k = 9
 
-        def local_topk(a, b, kk, off):
-            v, i = R.topk_bmm(a, b, k=kk, dim=2)
-            return v, torch.where(i >= 0, i + off, i)
+        def local_packed(a, b, kk):
+            v, i = R.topk_bmm(a, b, k=kk, dim=2)   # shard-local columns, -1 in empty slots
+            return S.pack_candidates(v, i)
 
-        # column shards + one all-gather + merge
+        # column shards + ONE all-gather of packed candidates + merge
         B_loc, off = S.column_shard(B)
-        v, i = S.topk_bmm_column_sharded(A, B_loc.contiguous(), off, k, local_topk, merge=S.merge_candidates_torch)
+        stride = S.shard_stride(B.shape[2], world, 128)
+        assert off == rank * stride
+        v, i = S.topk_bmm_column_sharded(A, B_loc.contiguous(), stride, k, local_packed, merge=S.merge_packed_torch)
         R.check_topk(v, i, A, B, k, 2)
         wv, _ = R.topk_bmm(A, B, k=k, dim=2)
         assert torch.equal(v, wv)
+
+        # a rank whose local step fails: nobody enters the all-gather, nobody merges
+        merges = []
+
+        def failing(a, b, kk):
+            if rank == 1:
+                raise RuntimeError("local top-k failed on purpose")
+            return local_packed(a, b, kk)
+
+        def counting_merge(*args):
+            merges.append(1)
+            return S.merge_packed_torch(*args)
+
+        try:
+            S.topk_bmm_column_sharded(A, B_loc.contiguous(), stride, k, failing, merge=counting_merge)
+            raise AssertionError("the failure was not reported")
+        except S.PeerFailure:
+            assert rank == 0
+        except RuntimeError as e:
+            assert rank == 1 and "on purpose" in str(e)
+        assert not merges
+        # the group is still usable afterwards
+        v2, _ = S.topk_bmm_column_sharded(A, B_loc.contiguous(), stride, k, local_packed, merge=S.merge_packed_torch)
+        assert torch.equal(v2, wv)
 
         # row shards: no communication, concatenation of rank outputs is the full answer
         A_loc, r0 = S.row_shard(A)
