@@ -49,9 +49,9 @@ std::mutex g_mu;
 DeviceState g_dev[kMaxDevices];
 EncodeTiledFn g_encode = nullptr;
 
-template <int EPI, int E, bool AR, bool PS, bool PR>
+template <int EPI, int E, bool AR, bool PS, bool PR = false>
 int set_one_attr() {
-  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, AR, PS, PR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, AR, PS, 0, PR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kSmemLimit)));
   return FBMM_OK;
 }
@@ -59,16 +59,14 @@ int set_one_attr() {
 template <int EPI, int E>
 int set_smem_attr() {
   int rc;
-  if ((rc = set_one_attr<EPI, E, false, false, false>()) != FBMM_OK) return rc;
-  if ((rc = set_one_attr<EPI, E, true, false, false>()) != FBMM_OK) return rc;
-  if ((rc = set_one_attr<EPI, E, false, false, true>()) != FBMM_OK) return rc;
-  if ((rc = set_one_attr<EPI, E, true, false, true>()) != FBMM_OK) return rc;
+  if ((rc = set_one_attr<EPI, E, false, false>()) != FBMM_OK) return rc;
+  if ((rc = set_one_attr<EPI, E, true, false>()) != FBMM_OK) return rc;
   if (EPI == kEpiMin || EPI == kEpiTopk) {
     constexpr bool kPs = (EPI == kEpiMin || EPI == kEpiTopk);
-    if ((rc = set_one_attr<EPI, E, false, kPs, false>()) != FBMM_OK) return rc;
-    if ((rc = set_one_attr<EPI, E, true, kPs, false>()) != FBMM_OK) return rc;
-    if ((rc = set_one_attr<EPI, E, false, kPs, true>()) != FBMM_OK) return rc;
-    if ((rc = set_one_attr<EPI, E, true, kPs, true>()) != FBMM_OK) return rc;
+    if ((rc = set_one_attr<EPI, E, false, kPs>()) != FBMM_OK) return rc;
+    if ((rc = set_one_attr<EPI, E, true, kPs>()) != FBMM_OK) return rc;
+    if ((rc = set_one_attr<EPI, E, false, kPs, kPs>()) != FBMM_OK) return rc;
+    if ((rc = set_one_attr<EPI, E, true, kPs, kPs>()) != FBMM_OK) return rc;
   }
   return FBMM_OK;
 }
@@ -218,6 +216,40 @@ int make_tensor_map(CUtensorMap* map, const Operand& op, int k, int l, int box_r
   if (r != CUDA_SUCCESS) return fail(FBMM_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
   tensor_map_remember(key, *map);
   return FBMM_OK;
+}
+
+// Tensor map over a uint8 mask [l or 1][rows][cols] (cols contiguous), box (box_cols, box_rows, 1),
+// no swizzle. cols must be a multiple of 16 and the base 16-byte aligned.
+int make_mask_map(CUtensorMap* map, const unsigned char* ptr, int rows, int cols, int l, bool shared, int box_rows,
+                  int box_cols) {
+  const TensorMapKey key{ptr, cols, shared ? 0 : static_cast<long long>(rows) * cols, rows, box_cols, l, box_rows, 4};
+  if (tensor_map_lookup(key, map)) return FBMM_OK;
+  const bool one_batch = shared || l == 1;
+  cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows), one_batch ? 1u : static_cast<cuuint64_t>(l)};
+  cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1};
+  cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows) * static_cast<cuuint64_t>(cols)};
+  cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<unsigned char*>(ptr), dims, strides, box,
+                              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FBMM_ERR_CUDA, "cuTensorMapEncodeTiled (mask) failed with CUresult %d", static_cast<int>(r));
+  tensor_map_remember(key, *map);
+  return FBMM_OK;
+}
+
+// The mask epilogue takes its element and thread masks through shared memory by TMA when
+// their rows can be addressed that way: n a multiple of 128 (element rows of n bytes and
+// thread rows of n / 8 bytes are then multiples of 16) and both bases 16-byte aligned.
+bool masks_fit_tma(const EpiArgs& e, int n) {
+  return n % 128 == 0 && (reinterpret_cast<uintptr_t>(e.element_mask) & 15u) == 0 &&
+         (reinterpret_cast<uintptr_t>(e.thread_mask) & 15u) == 0;
+}
+
+int make_mask_maps(CUtensorMap* em, CUtensorMap* tm, const EpiArgs& e, int l, int m, int n) {
+  const bool shared = e.em_stride == 0;
+  int rc;
+  if ((rc = make_mask_map(em, e.element_mask, m, n, l, shared, kTileM, kTileN)) != FBMM_OK) return rc;
+  return make_mask_map(tm, e.thread_mask, (m + 7) / 8, n / 8, l, shared, kTileM / 8, kTileN / 8);
 }
 
 int parse_layout(int letter, bool* transposed) {
@@ -377,31 +409,29 @@ int check_distance(int distance) {
   return FBMM_OK;
 }
 
-// CTA pairs (clusters of two, tcgen05 cta_group::2) work on 256-row blocks; with 128 rows
-// or fewer the second CTA would have nothing to do. The pair kernels give the same results
-// as the single-CTA ones but are not faster yet, so they run only when FBMM_PAIRS=1 is set
-// in the environment (read once per process).
-bool use_pairs(int rows) {
-  static const bool enabled = [] {
-    const char* e = getenv("FBMM_PAIRS");
-    return e != nullptr && e[0] == '1';
-  }();
-  return enabled && rows > kTileM;
-}
-
-// Workers that walk the unit list: SMs, or SM pairs.
-int unit_workers(int sms, int rows) { return use_pairs(rows) ? sms / 2 : sms; }
+// CTA pairs (clusters of two, tcgen05 cta_group::2; see the kernel's PAIR notes) work on
+// 256-row blocks and need pre-split planes: they are what the reducing ops run on whenever
+// the caller's workspace has room for the planes.
+// Measured against the single-CTA pre-split kernels (same operands, one B200): K = 128 (4 k-blocks
+// per tile) and K = 256 (A streams) run 2-3 % faster as pairs; K = 64 runs 25 % slower, because
+// with two k-blocks per tile the accumulator hand-off between the issuing CTA and BOTH epilogues
+// (one of them across the cluster) comes round too often. Pairs are used from K = 65 up.
+bool pairs_apply(const RowProblem& p, bool presplit) { return presplit && p.M > kTileM && p.K > 2 * kKBlock; }
+int rows_per_block(bool pairs) { return pairs ? 2 * kTileM : kTileM; }
+int unit_workers(int sms, bool pairs) { return pairs ? sms / 2 : sms; }
 
 // Launches the fused kernel. `lo_scratch` (or null) is room for the lo planes of both
 // operands (presplit_bytes): when given, they are computed here by one element-wise pass
-// each and the kernel runs without its splitter stage.
+// each and the kernel runs without its splitter stage, as CTA pairs if `pairs` (the shape
+// must then have been laid out in 256-row blocks).
 template <int EPI, int E>
 int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p, GemmShape shape, const EpiArgs& epi,
-                void* lo_scratch = nullptr) {
+                void* lo_scratch = nullptr, bool pairs = false) {
   CUtensorMap ta, tb, ta_lo, tb_lo;
   int rc;
-  const bool pairs = use_pairs(p.M);
-  const int b_box = pairs ? kTileN / 2 : kTileN;  // a CTA of a pair fetches half of each B tile
+  EpiArgs epi_args = epi;
+  if (pairs && lo_scratch == nullptr) return fail(FBMM_ERR_INVALID, "internal: pair kernels need pre-split planes");
+  const int b_box = pairs ? kTileN / 2 : kTileN;  // the pair kernels fetch B in pieces of 64 columns
   if ((rc = make_tensor_map(&ta, p.a, p.K, p.L, kTileM)) != FBMM_OK) return rc;
   const bool presplit = lo_scratch != nullptr && (EPI == kEpiMin || EPI == kEpiTopk);
   if (presplit) {
@@ -446,12 +476,18 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
     ta_lo = ta;
     tb_lo = tb;
   }
-  const int workers = unit_workers(st.sms, p.M);
+  const int workers = unit_workers(st.sms, pairs);
   const long long active = shape.num_units < workers ? shape.num_units : workers;
   const int kblocks = (p.K + kKBlock - 1) / kKBlock;
   // Up to K = 128 the row block of A stays in shared memory for the whole unit.
   const bool a_resident = a_stays_resident(p.K);
-  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, pairs);
+  // mask tiles by TMA when the masks allow it (the kernel reads them from global memory otherwise)
+  CUtensorMap tem = ta, ttm = ta;
+  if (EPI == kEpiMask && masks_fit_tma(epi, p.N)) {
+    if ((rc = make_mask_maps(&tem, &ttm, epi, p.L, p.M, p.N)) != FBMM_OK) return rc;
+    epi_args.mask_tma = 1;
+  }
+  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, 2u, epi_args.mask_tma != 0, pairs);
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
   // min / top-k have pre-split variants; store / mask never use them
   constexpr bool kHasPresplit = (EPI == kEpiMin || EPI == kEpiTopk);
@@ -469,27 +505,26 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
   cfg.attrs = attr;
   cfg.numAttrs = 1;
 #define FBMM_LAUNCH(AR, PS, PR) \
-  FBMM_CUDA(cudaLaunchKernelEx(&cfg, fbmm_gemm_kernel<EPI, E, AR, PS, PR>, ta, tb, ta_lo, tb_lo, shape, epi))
-  if (pairs) {
-    if (a_resident) { if (ps) FBMM_LAUNCH(true, kHasPresplit, true); else FBMM_LAUNCH(true, false, true); }
-    else            { if (ps) FBMM_LAUNCH(false, kHasPresplit, true); else FBMM_LAUNCH(false, false, true); }
+  FBMM_CUDA(cudaLaunchKernelEx(&cfg, fbmm_gemm_kernel<EPI, E, AR, PS, 0, PR>, ta, tb, ta_lo, tb_lo, tem, ttm, shape, epi_args))
+  if (ps && pairs) {
+    if (a_resident) FBMM_LAUNCH(true, kHasPresplit, kHasPresplit); else FBMM_LAUNCH(false, kHasPresplit, kHasPresplit);
+  } else if (a_resident) {
+    if (ps) FBMM_LAUNCH(true, kHasPresplit, false); else FBMM_LAUNCH(true, false, false);
   } else {
-    if (a_resident) { if (ps) FBMM_LAUNCH(true, kHasPresplit, false); else FBMM_LAUNCH(true, false, false); }
-    else            { if (ps) FBMM_LAUNCH(false, kHasPresplit, false); else FBMM_LAUNCH(false, false, false); }
+    if (ps) FBMM_LAUNCH(false, kHasPresplit, false); else FBMM_LAUNCH(false, false, false);
   }
 #undef FBMM_LAUNCH
   return FBMM_OK;
 }
 
-GemmShape base_shape(const RowProblem& p) {
+GemmShape base_shape(const RowProblem& p, bool pairs = false) {
   GemmShape s{};
   s.L = p.L; s.M = p.M; s.N = p.N; s.K = p.K;
   s.a_mn = p.a.mn_major ? 1 : 0;
   s.b_mn = p.b.mn_major ? 1 : 0;
   s.a_bcast = is_broadcast(p.a, p.L) ? 1 : 0;
   s.b_bcast = is_broadcast(p.b, p.L) ? 1 : 0;
-  const int rows_per_block = use_pairs(p.M) ? 2 * kTileM : kTileM;
-  s.m_blocks = (p.M + rows_per_block - 1) / rows_per_block;
+  s.m_blocks = (p.M + rows_per_block(pairs) - 1) / rows_per_block(pairs);
   s.n_tiles = (p.N + kTileN - 1) / kTileN;
   return s;
 }
@@ -508,6 +543,14 @@ int fbmm_version(void) { return 1000; }
 int fbmm_debug_read_profile(long long* out) {
   FBMM_CUDA(cudaDeviceSynchronize());
   FBMM_CUDA(cudaMemcpyFromSymbol(out, fbmm::g_fbmm_prof, 24 * sizeof(long long)));
+  return FBMM_OK;
+}
+// Tuning builds only: the tile timeline of CTA 0 (4 roles x 1024 stamps); clears it afterwards.
+int fbmm_debug_read_trace(long long* out) {
+  FBMM_CUDA(cudaDeviceSynchronize());
+  FBMM_CUDA(cudaMemcpyFromSymbol(out, fbmm::g_fbmm_trace, 4 * 1024 * sizeof(long long)));
+  static long long zeros[4 * 1024];
+  FBMM_CUDA(cudaMemcpyToSymbol(fbmm::g_fbmm_trace, zeros, sizeof(zeros)));
   return FBMM_OK;
 }
 #endif
@@ -540,7 +583,7 @@ int fbmm_bmm_f32(void* stream, const float* A, int a_layout, long long lda, long
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, p.M), kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   EpiArgs e{};
   e.C = C; e.ldc = ldc; e.stride_c = stride_c;
@@ -564,7 +607,7 @@ int fbmm_mbmm_f32(void* stream, const float* A, int a_layout, long long lda, lon
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, p.M), kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kStoreOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   EpiArgs e{};
   e.C = C; e.ldc = ldc; e.stride_c = stride_c;
@@ -605,8 +648,14 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   if ((reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 16-byte aligned");
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
-  GemmShape s = base_shape(p);
-  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, p.M), kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  // room behind the op's own scratch for the lo planes? then the operands are split once up
+  // front and the kernel runs as CTA pairs on 256-row blocks
+  const size_t lo_off = align_up(need, 256);
+  const bool presplit = presplit_worthwhile(p) && (b_planes_fit_l2(p) || p.L == 1) && workspace_bytes >= lo_off + presplit_bytes(p);
+  const bool pairs = pairs_apply(p, presplit);
+  GemmShape s = base_shape(p, pairs);
+  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, pairs), kMinOverheadTiles, kMaxChunks, &s.n_chunks,
+                &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   const long long rows = static_cast<long long>(l) * p.M;
   unsigned long long* keys = static_cast<unsigned long long*>(workspace);
@@ -616,10 +665,8 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   if (distance == FBMM_DIST_L2 &&
       (rc = launch_norms(stream, p, static_cast<char*>(workspace) + align_up(static_cast<size_t>(rows) * 8, 256), &e)) != FBMM_OK)
     return rc;
-  // room behind the op's own scratch for the lo planes? then the operands are split once up front
   void* lo_scratch = nullptr;
-  const size_t lo_off = align_up(need, 256);
-  if (presplit_worthwhile(p) && (b_planes_fit_l2(p) || p.L == 1) && workspace_bytes >= lo_off + presplit_bytes(p)) {
+  if (presplit) {
     lo_scratch = static_cast<char*>(workspace) + lo_off;
     // B's two planes should stay in L2 while every row block passes over them. What L2
     // keeps of data that all SMs share is about half its size, so wider B is swept in
@@ -637,7 +684,7 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
       s.chunk_major = 1;
     }
   }
-  if ((rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e, lo_scratch)) != FBMM_OK) return rc;
+  if ((rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e, lo_scratch, pairs)) != FBMM_OK) return rc;
   const int threads = 256;
   const long long blocks = (rows + threads - 1) / threads;
   fbmm_min_finalize_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(keys, values, indices, rows);
@@ -656,14 +703,6 @@ size_t fbmm_presplit_workspace_bytes(int l, int m, int n, int k, int dim, int a_
   return presplit_bytes(p);
 }
 
-static void topk_plan(int l, int rows_per_batch, int cols, int sms, int* n_chunks, int* tiles_per_chunk) {
-  const int rows_per_block = use_pairs(rows_per_batch) ? 2 * kTileM : kTileM;
-  const int m_blocks = (rows_per_batch + rows_per_block - 1) / rows_per_block;
-  sms = unit_workers(sms, rows_per_batch);
-  const int n_tiles = (cols + kTileN - 1) / kTileN;
-  choose_chunks(l, m_blocks, n_tiles, sms, kTopkOverheadTiles, kMaxChunks, n_chunks, tiles_per_chunk);
-}
-
 // Running lists of the units in flight: one area per CTA (at most one CTA per SM), 32 E
 // entries x 128 rows of fp32 values and as many int32 columns.
 static size_t topk_scratch_bytes(int sms, int topk) {
@@ -672,7 +711,7 @@ static size_t topk_scratch_bytes(int sms, int topk) {
 }
 
 // Pacing of a one-chunk sweep (GemmShape::pace_tiles): ranges of about 16 MB of the column
-// operand's two planes, and one counter per range and per unit a CTA works through.
+// operand's two planes, and one counter per range and per unit a worker goes through.
 struct PacePlan {
   int tiles;
   size_t count_bytes;
@@ -687,24 +726,48 @@ static PacePlan pace_plan(int l, int m_blocks, int n_tiles, int k, int workers) 
   return pp;
 }
 
+// Work split and workspace layout of one top-k call, for single CTAs (128-row blocks) or CTA
+// pairs (256-row blocks): [per-chunk lists, only when a row block's columns are cut into
+// chunks][squared norms, l2 only][running lists of the CTAs][pacing counters, one chunk only].
+struct TopkLayout {
+  int m_blocks, n_tiles, n_chunks, tiles_per_chunk;
+  size_t lists_values_bytes, lists_bytes, norms_off, scratch_off, pace_off, own;
+  PacePlan pace;
+};
+static TopkLayout topk_layout(int l, int rows_pb, int cols, int k, int topk, int distance, int sms, bool pairs) {
+  TopkLayout lay{};
+  lay.m_blocks = (rows_pb + rows_per_block(pairs) - 1) / rows_per_block(pairs);
+  lay.n_tiles = (cols + kTileN - 1) / kTileN;
+  choose_chunks(l, lay.m_blocks, lay.n_tiles, unit_workers(sms, pairs), kTopkOverheadTiles, kMaxChunks, &lay.n_chunks,
+                &lay.tiles_per_chunk);
+  size_t at = 0;
+  if (lay.n_chunks > 1) {
+    const size_t entries = static_cast<size_t>(lay.n_chunks) * l * rows_pb * topk;
+    lay.lists_values_bytes = align_up(entries * sizeof(float), 256);
+    lay.lists_bytes = align_up(lay.lists_values_bytes + entries * sizeof(long long), 256);
+    at = lay.lists_bytes;
+  }
+  lay.norms_off = at;
+  if (distance == FBMM_DIST_L2) at += align_up(static_cast<size_t>(l) * rows_pb * 4, 256) + align_up(static_cast<size_t>(l) * cols * 4, 256);
+  lay.scratch_off = at;
+  at += topk_scratch_bytes(sms, topk);
+  lay.pace_off = at;
+  if (lay.n_chunks == 1) {
+    lay.pace = pace_plan(l, lay.m_blocks, lay.n_tiles, k, unit_workers(sms, pairs));
+    at += lay.pace.count_bytes;
+  }
+  lay.own = at;
+  return lay;
+}
+
 size_t fbmm_topk_bmm_workspace_bytes(int l, int m, int n, int k, int topk, int dim, int distance) {
   if (l <= 0 || m <= 0 || n <= 0 || topk <= 0) return 0;
   const int rows_pb = dim == 1 ? n : m, cols = dim == 1 ? m : n;
-  int n_chunks, tpc;
-  topk_plan(l, rows_pb, cols, sm_count_or_default(), &n_chunks, &tpc);
-  size_t need = 0;
-  if (n_chunks > 1) {
-    const size_t entries = static_cast<size_t>(n_chunks) * l * rows_pb * topk;
-    need = align_up(entries * sizeof(float), 256) + entries * sizeof(long long);
-  }
-  if (distance == FBMM_DIST_L2)
-    need = align_up(need, 256) + align_up(static_cast<size_t>(l) * m * 4, 256) + align_up(static_cast<size_t>(l) * n * 4, 256);
-  need = align_up(need, 256) + topk_scratch_bytes(sm_count_or_default(), topk);
-  if (n_chunks == 1) {
-    const int sms = sm_count_or_default();
-    need += pace_plan(l, (rows_pb + kTileM - 1) / kTileM, (cols + kTileN - 1) / kTileN, k, sms).count_bytes;
-  }
-  return need;
+  const int sms = sm_count_or_default();
+  // which of the two layouts the call uses depends on the room it is given: enough for either
+  const size_t single = topk_layout(l, rows_pb, cols, k, topk, distance, sms, false).own;
+  const size_t pair = rows_pb > kTileM ? topk_layout(l, rows_pb, cols, k, topk, distance, sms, true).own : 0;
+  return std::max(single, pair);
 }
 
 }  // extern "C"
@@ -743,22 +806,29 @@ int topk_bmm_impl(cudaStream_t stream, const float* A, int a_layout, long long l
     return fail(FBMM_ERR_INVALID, "column indices (offset %lld + %d columns) must stay below 2^31 - 1", index_offset, p.N);
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
-  GemmShape s = base_shape(p);
-  topk_plan(l, p.M, p.N, st->sms, &s.n_chunks, &s.tiles_per_chunk);
+  if (workspace == nullptr) return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs a workspace");
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
+  // CTA pairs on pre-split planes when the workspace has room for the planes behind the op's
+  // own scratch; a column operand wider than L2 also needs the one-chunk sweep, which can be paced
+  TopkLayout lay = topk_layout(l, p.M, p.N, k, topk, distance, st->sms, true);
+  const bool presplit = p.M > kTileM && presplit_worthwhile(p) && (b_planes_fit_l2(p) || lay.n_chunks == 1) &&
+                        workspace_bytes >= lay.own + presplit_bytes(p);
+  const bool pairs = pairs_apply(p, presplit);
+  if (!pairs) lay = topk_layout(l, p.M, p.N, k, topk, distance, st->sms, false);
+  if (workspace_bytes < lay.own)
+    return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", lay.own, workspace_bytes);
+  GemmShape s = base_shape(p, pairs);
+  s.n_chunks = lay.n_chunks;
+  s.tiles_per_chunk = lay.tiles_per_chunk;
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   const long long rows = static_cast<long long>(l) * p.M;
+  char* ws = static_cast<char*>(workspace);
   EpiArgs e{};
   e.k = topk;
   e.index_offset = index_offset;
   if (s.n_chunks > 1) {
-    const size_t entries = static_cast<size_t>(s.n_chunks) * rows * topk;
-    const size_t need = align_up(entries * sizeof(float), 256) + entries * sizeof(long long);
-    if (workspace == nullptr || workspace_bytes < need)
-      return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
-    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
-      return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
-    e.topk_values = static_cast<float*>(workspace);
-    e.topk_indices = reinterpret_cast<long long*>(static_cast<char*>(workspace) + align_up(entries * sizeof(float), 256));
+    e.topk_values = reinterpret_cast<float*>(ws);
+    e.topk_indices = reinterpret_cast<long long*>(ws + lay.lists_values_bytes);
     e.topk_chunk_rows = rows;
   } else {
     e.topk_values = values;
@@ -766,54 +836,21 @@ int topk_bmm_impl(cudaStream_t stream, const float* A, int a_layout, long long l
     e.topk_packed = packed;
     e.topk_chunk_rows = 0;
   }
-  size_t own = 0;
-  if (s.n_chunks > 1) {
-    const size_t entries = static_cast<size_t>(s.n_chunks) * rows * topk;
-    own = align_up(align_up(entries * sizeof(float), 256) + entries * sizeof(long long), 256);
-  }
-  if (distance == FBMM_DIST_L2) {
-    const size_t need = own + norms_bytes(p);
-    if (workspace == nullptr || workspace_bytes < need)
-      return fail(FBMM_ERR_WORKSPACE, "topk_bmm with l2 distance needs %zu workspace bytes, got %zu", need, workspace_bytes);
-    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
-      return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
-    if ((rc = launch_norms(stream, p, static_cast<char*>(workspace) + own, &e)) != FBMM_OK) return rc;
-    own = need;
-  }
-  {
-    const size_t need = own + topk_scratch_bytes(st->sms, topk);
-    if (workspace == nullptr || workspace_bytes < need)
-      return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", need, workspace_bytes);
-    if ((reinterpret_cast<uintptr_t>(workspace) & 255u) != 0)
-      return fail(FBMM_ERR_ALIGN, "workspace is not 256-byte aligned");
-    e.topk_scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + own);
-    own = need;
-  }
-  // One chunk per row block and a column operand wider than L2: the sweep can be paced,
-  // which is what makes pre-split planes of any size affordable.
-  const bool can_pace = s.n_chunks == 1 && !use_pairs(p.M);
-  unsigned int* pace_counts = nullptr;
-  PacePlan pp{};
-  if (s.n_chunks == 1) {
-    pp = pace_plan(l, (p.M + kTileM - 1) / kTileM, s.n_tiles, p.K, st->sms);
-    if (workspace_bytes < own + pp.count_bytes)
-      return fail(FBMM_ERR_WORKSPACE, "topk_bmm needs %zu workspace bytes, got %zu", own + pp.count_bytes, workspace_bytes);
-    pace_counts = reinterpret_cast<unsigned int*>(static_cast<char*>(workspace) + own);
-    own += pp.count_bytes;
-  }
+  if (distance == FBMM_DIST_L2 && (rc = launch_norms(stream, p, ws + lay.norms_off, &e)) != FBMM_OK) return rc;
+  e.topk_scratch = reinterpret_cast<float*>(ws + lay.scratch_off);
   void* lo_scratch = nullptr;
-  if (presplit_worthwhile(p) && (b_planes_fit_l2(p) || can_pace) && workspace_bytes >= own + presplit_bytes(p)) {
-    lo_scratch = static_cast<char*>(workspace) + own;
+  if (presplit) {
+    lo_scratch = ws + lay.own;
     if (!b_planes_fit_l2(p)) {
-      s.pace_tiles = pp.tiles;
+      s.pace_tiles = lay.pace.tiles;
       s.pace_slack = 2;
-      s.pace_counts = pace_counts;
-      FBMM_CUDA(cudaMemsetAsync(pace_counts, 0, pp.count_bytes, stream));
+      s.pace_counts = reinterpret_cast<unsigned int*>(ws + lay.pace_off);
+      FBMM_CUDA(cudaMemsetAsync(s.pace_counts, 0, lay.pace.count_bytes, stream));
     }
   }
-  if (topk <= 32) rc = launch_gemm<kEpiTopk, 1>(stream, *st, p, s, e, lo_scratch);  // E: blocks of 32 list entries per row
-  else if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch);
-  else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e, lo_scratch);
+  if (topk <= 32) rc = launch_gemm<kEpiTopk, 1>(stream, *st, p, s, e, lo_scratch, pairs);  // E: blocks of 32 list entries per row
+  else if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch, pairs);
+  else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e, lo_scratch, pairs);
   if (rc != FBMM_OK) return rc;
   if (s.n_chunks > 1) {
     MergeIO io{};
@@ -1074,7 +1111,7 @@ extern "C" int fbmm_min_bmm_f32_noalloc(void* stream_, const float* A, int a_lay
   unsigned long long* keys = nullptr;
   if ((rc = noalloc_keys_for_current_device(&keys)) != FBMM_OK) return rc;
   GemmShape s = base_shape(p);
-  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, p.M), kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
+  choose_chunks(l, s.m_blocks, s.n_tiles, st->sms, kMinOverheadTiles, kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   // The array keeps the previous call's keys: every key this call will reduce into must
   // start at all-ones again.
@@ -1133,11 +1170,11 @@ int make_tensor_map_x16(CUtensorMap* map, const Operand& op, int k, int l, int b
 }
 
 template <int EPI, int E, bool AR, int DT>
-int launch_one_x16(const cudaLaunchConfig_t& cfg, const CUtensorMap& ta, const CUtensorMap& tb, const GemmShape& shape,
-                   const EpiArgs& epi) {
-  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, AR, true, false, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+int launch_one_x16(const cudaLaunchConfig_t& cfg, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tem,
+                   const CUtensorMap& ttm, const GemmShape& shape, const EpiArgs& epi) {
+  FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, AR, true, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kSmemLimit)));
-  FBMM_CUDA(cudaLaunchKernelEx(&cfg, fbmm_gemm_kernel<EPI, E, AR, true, false, DT>, ta, tb, ta, tb, shape, epi));
+  FBMM_CUDA(cudaLaunchKernelEx(&cfg, fbmm_gemm_kernel<EPI, E, AR, true, DT>, ta, tb, ta, tb, tem, ttm, shape, epi));
   return FBMM_OK;
 }
 
@@ -1152,23 +1189,24 @@ int launch_gemm_x16(cudaStream_t stream, const DeviceState& st, const RowProblem
   const long long active = shape.num_units < st.sms ? shape.num_units : st.sms;
   const int kblocks = (p.K + 2 * kKBlock - 1) / (2 * kKBlock);  // 64 elements per k-block
   const bool a_resident = kblocks <= kMaxResidentKBlocks;
-  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, false, 1u);
+  EpiArgs epi_args = epi;
+  CUtensorMap tem = ta, ttm = ta;
+  if (EPI == kEpiMask && masks_fit_tma(epi, p.N)) {
+    if ((rc = make_mask_maps(&tem, &ttm, epi, p.L, p.M, p.N)) != FBMM_OK) return rc;
+    epi_args.mask_tma = 1;
+  }
+  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, 1u, epi_args.mask_tma != 0);
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>(active), 1, 1);
   cfg.blockDim = dim3(block_threads(EPI), 1, 1);
   cfg.dynamicSmemBytes = plan.total;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 1;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
   if (dtype == FBMM_F16)
-    return a_resident ? launch_one_x16<EPI, E, true, 1>(cfg, ta, tb, shape, epi) : launch_one_x16<EPI, E, false, 1>(cfg, ta, tb, shape, epi);
-  return a_resident ? launch_one_x16<EPI, E, true, 2>(cfg, ta, tb, shape, epi) : launch_one_x16<EPI, E, false, 2>(cfg, ta, tb, shape, epi);
+    return a_resident ? launch_one_x16<EPI, E, true, 1>(cfg, ta, tb, tem, ttm, shape, epi_args)
+                      : launch_one_x16<EPI, E, false, 1>(cfg, ta, tb, tem, ttm, shape, epi_args);
+  return a_resident ? launch_one_x16<EPI, E, true, 2>(cfg, ta, tb, tem, ttm, shape, epi_args)
+                    : launch_one_x16<EPI, E, false, 2>(cfg, ta, tb, tem, ttm, shape, epi_args);
 }
 
 // Row-form problem of two k-contiguous 16-bit operands, checked.
@@ -1182,12 +1220,7 @@ int make_row_problem_x16(RowProblem* p, const void* A, long long lda, long long 
   return check_operand_x16("B", dim == 2 ? p->b : p->a, k, l);
 }
 
-// shape with 128-row blocks whatever the pair setting of the fp32 kernels
-GemmShape base_shape_x16(const RowProblem& p) {
-  GemmShape s = base_shape(p);
-  s.m_blocks = (p.M + kTileM - 1) / kTileM;
-  return s;
-}
+GemmShape base_shape_x16(const RowProblem& p) { return base_shape(p); }
 
 // Squared norms of both 16-bit operands into `scratch` (norms_bytes); fills the epilogue arguments.
 int launch_norms_x16(cudaStream_t stream, const RowProblem& p, void* scratch, EpiArgs* e, int dtype) {
@@ -1271,30 +1304,26 @@ extern "C" int fbmm_topk_bmm_x16(void* stream_, const void* A, long long lda, lo
   DeviceState* st;
   if ((rc = device_state(&st)) != FBMM_OK) return rc;
   GemmShape s = base_shape_x16(p);
-  // the same chunking as the workspace query assumed (which follows the fp32 kernels)
-  topk_plan(l, p.M, p.N, st->sms, &s.n_chunks, &s.tiles_per_chunk);
+  const TopkLayout lay = topk_layout(l, p.M, p.N, k, topk, distance, st->sms, false);
+  s.n_chunks = lay.n_chunks;
+  s.tiles_per_chunk = lay.tiles_per_chunk;
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   const long long rows = static_cast<long long>(l) * p.M;
+  char* ws = static_cast<char*>(workspace);
   EpiArgs e{};
   e.k = topk;
   e.index_offset = index_offset;
-  size_t own = 0;
   if (s.n_chunks > 1) {
-    const size_t entries = static_cast<size_t>(s.n_chunks) * rows * topk;
-    e.topk_values = static_cast<float*>(workspace);
-    e.topk_indices = reinterpret_cast<long long*>(static_cast<char*>(workspace) + align_up(entries * sizeof(float), 256));
+    e.topk_values = reinterpret_cast<float*>(ws);
+    e.topk_indices = reinterpret_cast<long long*>(ws + lay.lists_values_bytes);
     e.topk_chunk_rows = rows;
-    own = align_up(align_up(entries * sizeof(float), 256) + entries * sizeof(long long), 256);
   } else {
     e.topk_values = values;
     e.topk_indices = indices;
     e.topk_chunk_rows = 0;
   }
-  if (distance == FBMM_DIST_L2) {
-    if ((rc = launch_norms_x16(stream, p, static_cast<char*>(workspace) + own, &e, dtype)) != FBMM_OK) return rc;
-    own += norms_bytes(p);
-  }
-  e.topk_scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + own);
+  if (distance == FBMM_DIST_L2 && (rc = launch_norms_x16(stream, p, ws + lay.norms_off, &e, dtype)) != FBMM_OK) return rc;
+  e.topk_scratch = reinterpret_cast<float*>(ws + lay.scratch_off);
   if (topk <= 32) rc = launch_gemm_x16<kEpiTopk, 1>(stream, *st, p, s, e, dtype);
   else if (topk <= 64) rc = launch_gemm_x16<kEpiTopk, 2>(stream, *st, p, s, e, dtype);
   else rc = launch_gemm_x16<kEpiTopk, 4>(stream, *st, p, s, e, dtype);

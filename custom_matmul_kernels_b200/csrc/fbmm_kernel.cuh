@@ -5,9 +5,13 @@
 // kernels/minbmm.cu:348, kernels/topkbmm.cu:500 and their layout variants) with one
 // persistent, warp-specialised kernel:
 //
-//   warp 0      TMA producer: raw fp32 operand tiles -> shared-memory ring (for K <= 128 the
-//               128 x K block of A is loaded once per unit and stays resident while the
-//               unit's column tiles stream past)
+//   warp 0      TMA producer: raw fp32 operand tiles -> shared-memory ring
+//   last warp   A loader: for K <= 128 the 128 x K block of A is loaded once per unit and
+//               stays resident while the unit's column tiles stream past. It has a thread of
+//               its own so that the ring keeps running across unit boundaries: the next
+//               unit's B tiles are requested while the last tile of this unit is still being
+//               multiplied, and each k-block of the next A is requested the moment the last
+//               MMA that reads the old one has retired
 //   warps 2-5   splitters: lo = x - tf32(x), written beside the raw tile (the raw tile
 //               itself serves as the hi plane because the tensor core ignores the low
 //               13 mantissa bits of a tf32 operand)
@@ -24,8 +28,8 @@
 // units i, i + gridDim.x, ... All four roles walk the same unit list.
 //
 // Variants (template parameters of the kernel): lo planes taken from global memory
-// instead of the splitters (PRESPLIT), clusters of two CTAs on 256-row blocks (PAIR), and
-// fp16 / bf16 operands multiplied as they are by kind::f16 (DT).
+// instead of the splitters (PRESPLIT), and fp16 / bf16 operands multiplied as they are by
+// kind::f16 (DT).
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -51,7 +55,9 @@ enum EpilogueKind { kEpiStore = 0, kEpiMask = 1, kEpiMin = 2, kEpiTopk = 3 };
 // eight warps; the reducing epilogues keep one warp per row quarter because a row's state
 // has one owner.
 __host__ __device__ constexpr int epilogue_warps(int epi) { return epi == kEpiMask ? 8 : 4; }
-__host__ __device__ constexpr int block_threads(int epi) { return 192 + 32 * epilogue_warps(epi); }
+// warps: 0 ring producer, 1 MMA issuer, 2-5 splitters, then the epilogue warps, then one warp
+// that loads the resident A blocks
+__host__ __device__ constexpr int block_threads(int epi) { return 192 + 32 * epilogue_warps(epi) + 32; }
 
 // Device status word (bit 0: a bounded wait ran out).
 __device__ unsigned int g_fbmm_status[4];
@@ -59,12 +65,27 @@ __device__ unsigned int g_fbmm_status[4];
 // Optional per-role wait-time counters (cycles), compiled in only for tuning builds.
 #ifdef FBMM_PROFILE
 __device__ long long g_fbmm_prof[24];
+// timeline of CTA 0: per role a list of clock64() stamps (tile boundaries)
+__device__ long long g_fbmm_trace[4][1024];
+#define FBMM_TRACE_DECL int trace_n_ = 0, trace2_n_ = 0
+#define FBMM_TRACE2(role) if (blockIdx.x == 0 && trace2_n_ < 1024) g_fbmm_trace[role][trace2_n_++] = clock64()
+#define FBMM_TRACE(role) if (blockIdx.x == 0 && trace_n_ < 1024) g_fbmm_trace[role][trace_n_++] = clock64()
 #define FBMM_PROF_DECL long long prof_t0_ = 0, prof_acc_[4] = {0, 0, 0, 0}, prof_x_[4] = {0, 0, 0, 0}, prof_x0_ = 0
+#ifdef FBMM_PROFILE_LIGHT
+#define FBMM_PROF_XBEGIN()
+#define FBMM_PROF_XEND(i)
+#else
 #define FBMM_PROF_XBEGIN() prof_x0_ = clock64()
 #define FBMM_PROF_XEND(i) prof_x_[i] += clock64() - prof_x0_
+#endif
 #define FBMM_PROF_XFLUSH() if (blockIdx.x == 0) { for (int q_ = 0; q_ < 4; ++q_) g_fbmm_prof[16 + q_] = prof_x_[q_]; }
+#ifdef FBMM_PROFILE_LIGHT
+#define FBMM_PROF_BEGIN()
+#define FBMM_PROF_END(i)
+#else
 #define FBMM_PROF_BEGIN() prof_t0_ = clock64()
 #define FBMM_PROF_END(i) prof_acc_[i] += clock64() - prof_t0_
+#endif
 #define FBMM_PROF_MARK(i, c, n) long long prof_m0_ = clock64(); prof_acc_[c] += (n)
 #define FBMM_PROF_MARK_END(i) prof_acc_[i] += clock64() - prof_m0_
 #define FBMM_PROF_PHASE_DECL long long prof_p0_ = clock64()
@@ -79,6 +100,9 @@ __device__ long long g_fbmm_prof[24];
     for (int q_ = 0; q_ < 4; ++q_) g_fbmm_prof[(base) + q_] = prof_acc_[q_];            \
   }
 #else
+#define FBMM_TRACE_DECL
+#define FBMM_TRACE(role)
+#define FBMM_TRACE2(role)
 #define FBMM_PROF_DECL
 #define FBMM_PROF_XBEGIN()
 #define FBMM_PROF_XEND(i)
@@ -126,6 +150,8 @@ struct EpiArgs {
   const unsigned char* element_mask;  // [L or 1][M][N]
   long long bm_stride, tm_stride, em_stride;  // per-batch strides, 0 when shared
   int bm_cols, tm_cols;
+  int mask_tma;  // the element and thread masks of a tile come through shared memory by TMA (tensor maps
+                 // tmap_em / tmap_tm are valid: n a multiple of 128, mask bases 16-byte aligned)
   // min
   unsigned long long* keys;  // [L][M] packed (ordered value << 32 | column)
   // top-k
@@ -590,17 +616,27 @@ constexpr uint32_t kTopkStageBytes = kTopkStageSlots * kTileM * 8u;
 constexpr uint32_t kBarrierBytes = 512;
 constexpr uint32_t kSmemLimit = 232448;  // 227 KB per CTA on sm_100
 
+// Mask tiles of the mask epilogue (mbmm): the 128 x 128 element-mask bytes of a tile and its
+// 16 x 16 thread-mask bytes, brought in by TMA two tiles ahead of the epilogue, which would
+// otherwise wait out a trip to HBM for every chunk of every tile.
+constexpr uint32_t kMaskStages = 2;
+constexpr uint32_t kMaskElemBytes = kTileM * 128u;       // 128 rows x 128 columns, one byte each
+constexpr uint32_t kMaskThreadBytes = 16u * 16u;         // one byte per 8 x 8 tile
+constexpr uint32_t kMaskStageBytes = kMaskElemBytes + 512u;
+
 struct SmemPlan {
   uint32_t a_bytes, stage_bytes, stages, epi_bytes, total;
 };
-// `planes`: 2 for fp32 operands (hi and lo), 1 for 16-bit ones.
-__host__ __device__ inline SmemPlan make_smem_plan(bool a_resident, int kblocks, bool topk, bool pair,
-                                                   uint32_t planes = 2u) {
+// `planes`: 2 for fp32 operands (hi and lo), 1 for 16-bit ones. `epi_extra`: what the epilogue
+// keeps in shared memory (top-k staging, or the mask tiles).
+// `pair`: a CTA of a pair keeps one whole plane of each B tile plus half a plane (see PAIR below).
+__host__ __device__ inline SmemPlan make_smem_plan(bool a_resident, int kblocks, bool topk, uint32_t planes = 2u,
+                                                   bool mask_tiles = false, bool pair = false) {
   SmemPlan p;
-  const uint32_t b_plane = pair ? kPlaneBytes / 2u : kPlaneBytes;  // a CTA of a pair holds half of each B tile
+  const uint32_t b_bytes = pair ? kPlaneBytes + kPlaneBytes / 2u : planes * kPlaneBytes;
   p.a_bytes = a_resident ? static_cast<uint32_t>(kblocks) * planes * kPlaneBytes : 0u;
-  p.stage_bytes = (a_resident ? 0u : planes * kPlaneBytes) + planes * b_plane;
-  p.epi_bytes = topk ? kTopkStageBytes : 0u;
+  p.stage_bytes = (a_resident ? 0u : planes * kPlaneBytes) + b_bytes;
+  p.epi_bytes = topk ? kTopkStageBytes : (mask_tiles ? kMaskStages * kMaskStageBytes : 0u);
   const uint32_t fixed = p.a_bytes + p.epi_bytes + kBarrierBytes + 1024u /* alignment slack */;
   uint32_t st = (kSmemLimit - fixed) / p.stage_bytes;
   p.stages = st > static_cast<uint32_t>(kMaxStages) ? static_cast<uint32_t>(kMaxStages) : st;
@@ -617,6 +653,8 @@ struct Barriers {
   uint64_t a_full[kMaxResidentKBlocks];   // resident A k-block landed
   uint64_t a_split[kMaxResidentKBlocks];  // its lo plane written
   uint64_t a_empty[kMaxResidentKBlocks];  // last MMA of the unit done reading it
+  uint64_t mask_full[kMaskStages];        // mask tile landed
+  uint64_t mask_empty[kMaskStages];       // epilogue done reading it
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -639,45 +677,62 @@ __device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint
 // the ring, and a ring stage is ready the moment its copies land. A resident row block of
 // A is still split in shared memory (once per unit, so there is nothing to save).
 //
-// PAIR: the kernel runs as clusters of two CTAs on 256-row blocks. Each CTA loads, splits
-// and keeps its own 128 rows of A and HALF of every B tile (64 columns); the even CTA issues
-// tcgen05.mma.cta_group::2 (M = 256), which reads A and its half of B from each CTA's own
-// shared memory and writes each CTA's 128 accumulator rows into its own TMEM. Per SM that
-// halves the B bytes the tensor core pulls from shared memory and the B bytes TMA writes,
-// and in isolation N = 128 runs at 64 cycles per MMA instead of 88. Barriers that gate the
-// MMAs live in the even CTA (the peer arrives on them through the cluster window); commits
-// release both CTAs' stages. Results are identical to the single-CTA kernels; the whole
-// kernel is currently ~20 % slower than they are (the tensor pipe sits idle between pair
-// MMAs for a reason not yet found), so the library uses pairs only when asked to.
+// PAIR: the kernel runs as clusters of two CTAs on 256-row blocks, and the even CTA issues
+// tcgen05.mma.cta_group::2 for both. What limits the single-CTA kernel is not the tensor
+// core's arithmetic but the rate at which one thread can hand it instructions: an MMA costs
+// the issuing thread 65 cycles or more whatever its shape, and with K = 8 per tf32
+// instruction the 128 x 128 x 8 product (64 cycles of arithmetic) is issue-bound. A pair MMA
+// does the work of two: M = 256 (128 rows of A from each CTA's own shared memory, 128
+// accumulator rows in each CTA's own TMEM), and its N operand rows are taken half from each
+// CTA. The three tf32 products of a k-step then take two instructions for 256 x 128 outputs:
+//   wide    A_hi x [B_hi | B_lo], N = 256: the even CTA holds the tile's B_hi plane, the odd
+//           CTA its B_lo plane, at the same shared-memory offset, so the instruction's first
+//           128 result columns are hi*hi (the big accumulator) and the other 128 are hi*lo
+//           (the small one) in both CTAs;
+//   narrow  A_lo x B_hi, N = 128: the even CTA supplies columns 0-63 of B_hi, the odd CTA
+//           columns 64-127 (a second copy of 8 KB per CTA, at a common offset).
+// Measured on resident operands: 762 cycles per 256 x 128 x 32 k-block (4 wide + 4 narrow,
+// commits included) against 1057 per 128 x 128 x 32 in a single CTA, i.e. 2.8 times the
+// rate per SM. Each CTA loads its own operands (24 KB of B per k-block instead of 32 KB, no
+// cluster fan-out of any copy); completion bytes of both CTAs are counted on the even CTA's
+// barrier, barriers that gate the MMAs live in the even CTA (the peer arrives on them through
+// the cluster window) and every commit goes to both CTAs. Needs pre-split planes and fp32
+// operands; used by the reducing epilogues (min, top-k) for problems of more than 128 rows.
 //
 // DT: element type of the operands. 0 = fp32 (everything above). 1 = fp16, 2 = bf16: the
 // operands are multiplied as they are by tcgen05.mma.kind::f16 (fp32 accumulation), one MMA
 // per k-step into the big accumulator only; a k-block is 64 elements (still 128 bytes per
 // row), there are no lo planes and nothing to split, so these variants are instantiated with
-// PRESPLIT = true and PAIR = false and load the hi planes only. Both operands must be
-// k-contiguous. The lo-plane slots of the shared-memory plan stay unused.
-template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT, bool PAIR, int DT = 0>
+// PRESPLIT = true and load the hi planes only. Both operands must be k-contiguous. The
+// lo-plane slots of the shared-memory plan stay unused.
+template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT, int DT = 0, bool PAIR = false>
 __global__ void __launch_bounds__(block_threads(EPI), 1)
 fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_a_lo, const __grid_constant__ CUtensorMap tmap_b_lo,
+                 const __grid_constant__ CUtensorMap tmap_em, const __grid_constant__ CUtensorMap tmap_tm,
                  const GemmShape shape, const EpiArgs epi) {
   constexpr int TILE_N = kTileN;
   constexpr int kAccStages = 2;
   static_assert(2 * kAccStages * TILE_N <= kTmemCols, "TMEM budget");
 
   constexpr bool kHalf = DT != 0;
-  static_assert(!kHalf || (PRESPLIT && !PAIR), "16-bit variants: PRESPLIT = true, PAIR = false");
+  static_assert(!kHalf || PRESPLIT, "16-bit variants: PRESPLIT = true");
+  static_assert(!PAIR || (PRESPLIT && !kHalf && (EPI == kEpiMin || EPI == kEpiTopk)),
+                "pair variants: fp32 operands with pre-split planes, reducing epilogues");
   constexpr int kKElems = kHalf ? 2 * kKBlock : kKBlock;  // elements of K per k-block (128 bytes)
   const int kblocks = (shape.K + kKElems - 1) / kKElems;
   constexpr uint32_t kPlanes = kHalf ? 1u : 2u;  // planes per operand tile in shared memory
-  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, PAIR, kPlanes);
+  const bool mask_tma = EPI == kEpiMask && epi.mask_tma != 0;
+  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, kPlanes, mask_tma, PAIR);
   const uint32_t stages = plan.stages;
-  constexpr uint32_t kBPlane = PAIR ? kPlaneBytes / 2u : kPlaneBytes;  // this CTA's part of a B tile plane
-  constexpr int kBCols = PAIR ? TILE_N / 2 : TILE_N;                  // ... in columns
-  // offsets inside a ring stage
+  constexpr uint32_t kBPlane = kPlaneBytes;  // one plane of a B tile
+  // offsets inside a ring stage. Single CTA: (A hi | A lo |) B hi | B lo. Pair: (A hi | A lo |)
+  // this CTA's plane of the wide operand (B hi in the even CTA, B lo in the odd one) | its 64
+  // columns of B hi for the narrow MMA.
   const uint32_t off_a_hi = 0, off_a_lo = kPlaneBytes;
   const uint32_t off_b_hi = A_RES ? 0u : kPlanes * kPlaneBytes;
   const uint32_t off_b_lo = off_b_hi + kBPlane;
+  const uint32_t off_b_narrow = off_b_hi + kBPlane;  // pair only
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -700,17 +755,21 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     bars->abort_flag = 0;
     for (int s = 0; s < kMaxStages; ++s) {
       mbar_init(&bars->full[s], 1);
-      mbar_init(&bars->split[s], kSplitThreads * kCtas);
+      mbar_init(&bars->split[s], (kSplitThreads / 32) * kCtas);       // one arrival per splitter warp
       mbar_init(&bars->empty[s], 1);
     }
     for (int s = 0; s < kAccStages; ++s) {
       mbar_init(&bars->acc_full[s], 1);
-      mbar_init(&bars->acc_empty[s], 32 * epilogue_warps(EPI) * kCtas);
+      mbar_init(&bars->acc_empty[s], epilogue_warps(EPI) * kCtas);  // one arrival per epilogue warp
     }
     for (int s = 0; s < kMaxResidentKBlocks; ++s) {
       mbar_init(&bars->a_full[s], 1);
-      mbar_init(&bars->a_split[s], kSplitThreads * kCtas);
+      mbar_init(&bars->a_split[s], (kSplitThreads / 32) * kCtas);
       mbar_init(&bars->a_empty[s], 1);
+    }
+    for (int s = 0; s < static_cast<int>(kMaskStages); ++s) {
+      mbar_init(&bars->mask_full[s], 1);
+      mbar_init(&bars->mask_empty[s], epilogue_warps(EPI));
     }
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
@@ -718,6 +777,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (PRESPLIT && !kHalf) {
       tma_prefetch_desc(&tmap_a_lo);
       tma_prefetch_desc(&tmap_b_lo);
+    }
+    if (mask_tma) {
+      tma_prefetch_desc(&tmap_em);
+      tma_prefetch_desc(&tmap_tm);
     }
   }
   if (warp == 1) {
@@ -757,15 +820,9 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (mb128 * kTileM >= shape.M) return false;
     return epi.block_mask[b * epi.bm_stride + static_cast<long long>(mb128) * epi.bm_cols + t] != 0;
   };
-  // this CTA's own 128x128 block
-  auto tile_live_own = [&](int b, int mb, int t) -> bool {
-    if (EPI != kEpiMask) return true;
-    return block_live(b, PAIR ? mb * 2 + static_cast<int>(cta_rank) : mb, t);
-  };
-  // the tile as the loads and MMAs see it: for a pair, live when either block is
   auto tile_live = [&](int b, int mb, int t) -> bool {
     if (EPI != kEpiMask) return true;
-    return PAIR ? (block_live(b, mb * 2, t) || block_live(b, mb * 2 + 1, t)) : block_live(b, mb, t);
+    return block_live(b, mb, t);
   };
   // First and last live tile of a unit; false when the unit has none.
   auto live_range = [&](int b, int mb, int t0, int t1, int& first, int& last) -> bool {
@@ -780,14 +837,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // else in L2. A resident row block of A is read exactly once (first out); a streamed one
   // is re-read for every column tile of the unit and keeps the default priority.
   const uint64_t a_policy = A_RES ? kL2EvictFirst : kL2EvictLast;
-  // One TMA box. `bar` is the local barrier; with `to_leader` the completion bytes are
-  // counted on the same barrier of the pair's even CTA instead.
+  // One TMA box into this CTA's shared memory. `bar` is a local barrier; with `to_leader` the
+  // completion bytes are counted on the same barrier of the pair's even CTA instead.
   auto tma_issue = [&](uint8_t* dst, const CUtensorMap* map, uint64_t* bar, bool to_leader, int c0, int c1, int c2,
                        uint64_t policy) {
     if (PAIR && to_leader) tma_load_3d_pair(dst, map, bars_cta0 + bar_off(bar), c0, c1, c2, policy);
     else tma_load_3d(dst, map, bar, c0, c1, c2, policy);
   };
-  // this CTA's 128 rows of A, k-block kb
+  // this CTA's 128 rows of A of row block mb, k-block kb
   auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int mb, int b) {
     if (shape.a_bcast) b = 0;
     if (!shape.a_mn) {
@@ -798,24 +855,41 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tma_issue(dst + c * 4096, map, bar, to_leader, row_base(mb) + c * 32, kb * kKBlock, b, a_policy);
     }
   };
-  // this CTA's columns of B tile t (all 128, or its 64 of a pair), k-block kb
-  auto load_b = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int t, int b) {
-    const int col = t * TILE_N + static_cast<int>(cta_rank) * kBCols;
+  // `ncols` columns (a multiple of 32) of an operand plane of B starting at column `col`, k-block kb.
+  // K-major tensor maps of the pair kernels have boxes of 64 rows, the others of 128.
+  auto load_b_cols = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int col, int ncols,
+                         int b) {
     if (shape.b_bcast) b = 0;
     if (!shape.b_mn) {
-      tma_issue(dst, map, bar, to_leader, kb * kKElems, col, b, kL2EvictLast);
+      constexpr int kBox = PAIR ? TILE_N / 2 : TILE_N;
+      for (int c = 0; c < ncols; c += kBox)
+        tma_issue(dst + c * 128, map, bar, to_leader, kb * kKElems, col + c, b, kL2EvictLast);
     } else {
-#pragma unroll
-      for (int c = 0; c < kBCols / 32; ++c)
-        tma_issue(dst + c * 4096, map, bar, to_leader, col + c * 32, kb * kKBlock, b, kL2EvictLast);
+      for (int c = 0; c < ncols; c += 32)
+        tma_issue(dst + c * 128, map, bar, to_leader, col + c, kb * kKBlock, b, kL2EvictLast);
     }
+  };
+  // the 128 columns of B tile t, k-block kb (single CTA)
+  auto load_b = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, int kb, int t, int b) {
+    load_b_cols(map, dst, bar, false, kb, t * TILE_N, TILE_N, b);
   };
 
   // Barriers that gate the MMAs live in the pair's even CTA: the peer arrives through the
-  // cluster window, the issuer waits with cluster scope, and commits release both CTAs.
-  auto arrive_leader = [&](uint64_t* bar) {
-    if (PAIR) mbar_arrive_cluster(bars_cta0 + bar_off(bar)); else mbar_arrive(bar);
+  // cluster window, the issuer waits with cluster scope, and commits go to both CTAs.
+  // One arrival per warp, by lane 0 once every lane has got there: an arrival through the
+  // cluster window costs hundreds of cycles when 128 threads queue up for it.
+  auto warp_arrive = [&](uint64_t* bar) {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
   };
+  auto warp_arrive_leader = [&](uint64_t* bar) {
+    __syncwarp();
+    if (lane == 0) {
+      if (PAIR && cta_rank != 0) mbar_arrive_cluster(bars_cta0 + bar_off(bar)); else mbar_arrive(bar);
+    }
+  };
+  // every wait of a pair kernel whose arrivals can come through the cluster (the peer's
+  // arrivals, pair commits, the peer's copies) uses the cluster-scope form
   auto wait_gate = [&](uint64_t* bar, uint32_t parity) -> bool {
     return PAIR ? mbar_wait_cluster(bar, parity, abort_flag) : mbar_wait(bar, parity, abort_flag);
   };
@@ -831,7 +905,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t stage = 0, phase = 0, a_phase = 0;
+      uint32_t stage = 0, phase = 0, mstage = 0, mphase = 0;
       bool ok = true;
       FBMM_PROF_DECL;
       const long long prof_start = clock64();
@@ -843,7 +917,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!live_range(b, mb, t0, t1, first, last)) continue;
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
-          if (shape.pace_tiles > 0 && (t - t0) % shape.pace_tiles == 0) {
+          if (shape.pace_tiles > 0 && cta_rank == 0 && (t - t0) % shape.pace_tiles == 0) {
             if (pace_seq > 0) atomicAdd(shape.pace_counts + pace_seq - 1, 1u);  // the range before is requested
             if (pace_seq >= shape.pace_slack) {
               // CTAs that have a unit of the ordinal the awaited range belongs to
@@ -856,37 +930,51 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             ++pace_seq;
           }
+          if (mask_tma) {
+            // the tile's mask bytes, as soon as the epilogue has let go of the stage
+            ok = mbar_wait(&bars->mask_empty[mstage], mphase ^ 1u, abort_flag);
+            if (!ok) break;
+            uint8_t* ms = epi_smem + mstage * kMaskStageBytes;
+            const int mask_b = epi.em_stride == 0 ? 0 : b;  // shared masks have no batch axis
+            mbar_arrive_expect_tx(&bars->mask_full[mstage], kMaskElemBytes + kMaskThreadBytes);
+            tma_load_3d(ms, &tmap_em, &bars->mask_full[mstage], t * TILE_N, row_base(mb), mask_b, kL2EvictFirst);
+            tma_load_3d(ms + kMaskElemBytes, &tmap_tm, &bars->mask_full[mstage], t * (TILE_N / 8), row_base(mb) / 8,
+                        mask_b, kL2EvictFirst);
+            if (++mstage == kMaskStages) { mstage = 0; mphase ^= 1u; }
+          }
           for (int kb = 0; kb < kblocks; ++kb) {
-            if (A_RES && t == first) {
-              // the row block's A k-block, loaded once per unit as soon as the previous
-              // unit's last tile has finished with that k-block
-              ok = mbar_wait(&bars->a_empty[kb], a_phase ^ 1u, abort_flag);
-              if (!ok) break;
-              mbar_arrive_expect_tx(&bars->a_full[kb], kPlaneBytes);
-              load_a(&tmap_a, a_region + kb * kPlanes * kPlaneBytes + off_a_hi, &bars->a_full[kb], false, kb, mb, b);
-            }
             FBMM_PROF_BEGIN();
-            ok = mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag);
+            ok = wait_gate(&bars->empty[stage], phase ^ 1u);
             FBMM_PROF_END(0);
             if (!ok) break;
             uint8_t* sb = ring + stage * plan.stage_bytes;
-            // bytes this CTA brings into the stage
-            constexpr uint32_t kMyBytes = ((A_RES ? 0u : kPlaneBytes) + kBPlane) * ((PRESPLIT && !kHalf) ? 2u : 1u);
-            // With pre-split planes nothing stands between the copies and the MMAs, so a
-            // pair counts both CTAs' bytes on the even CTA's barrier, which that CTA arms.
-            constexpr bool kToLeader = PAIR && PRESPLIT;
-            if (!kToLeader) mbar_arrive_expect_tx(&bars->full[stage], kMyBytes);
-            else if (cta_rank == 0) mbar_arrive_expect_tx(&bars->full[stage], 2u * kMyBytes);
-            if (!A_RES) {
-              load_a(&tmap_a, sb + off_a_hi, &bars->full[stage], kToLeader, kb, mb, b);
-              if (PRESPLIT && !kHalf) load_a(&tmap_a_lo, sb + off_a_lo, &bars->full[stage], kToLeader, kb, mb, b);
+            if (PAIR) {
+              // each CTA brings its own operands; the even CTA's barrier counts the bytes of both
+              constexpr uint32_t kMyBytes = (A_RES ? 0u : 2u * kPlaneBytes) + kPlaneBytes + kPlaneBytes / 2u;
+              if (cta_rank == 0) mbar_arrive_expect_tx(&bars->full[stage], 2u * kMyBytes);
+              if (!A_RES) {
+                load_a(&tmap_a, sb + off_a_hi, &bars->full[stage], true, kb, mb, b);
+                load_a(&tmap_a_lo, sb + off_a_lo, &bars->full[stage], true, kb, mb, b);
+              }
+              const int col = t * TILE_N;
+              // wide operand: B hi in the even CTA, B lo in the odd one; narrow: this CTA's 64 columns of B hi
+              load_b_cols(cta_rank == 0 ? &tmap_b : &tmap_b_lo, sb + off_b_hi, &bars->full[stage], true, kb, col, TILE_N, b);
+              load_b_cols(&tmap_b, sb + off_b_narrow, &bars->full[stage], true, kb,
+                          col + static_cast<int>(cta_rank) * (TILE_N / 2), TILE_N / 2, b);
+            } else {
+              // bytes that land in the stage
+              constexpr uint32_t kStageTx = ((A_RES ? 0u : kPlaneBytes) + kBPlane) * ((PRESPLIT && !kHalf) ? 2u : 1u);
+              mbar_arrive_expect_tx(&bars->full[stage], kStageTx);
+              if (!A_RES) {
+                load_a(&tmap_a, sb + off_a_hi, &bars->full[stage], false, kb, mb, b);
+                if (PRESPLIT && !kHalf) load_a(&tmap_a_lo, sb + off_a_lo, &bars->full[stage], false, kb, mb, b);
+              }
+              load_b(&tmap_b, sb + off_b_hi, &bars->full[stage], kb, t, b);
+              if (PRESPLIT && !kHalf) load_b(&tmap_b_lo, sb + off_b_lo, &bars->full[stage], kb, t, b);
             }
-            load_b(&tmap_b, sb + off_b_hi, &bars->full[stage], kToLeader, kb, t, b);
-            if (PRESPLIT && !kHalf) load_b(&tmap_b_lo, sb + off_b_lo, &bars->full[stage], kToLeader, kb, t, b);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
         }
-        a_phase ^= 1u;
       }
       // the last range counts too: CTAs with one more unit wait for it
       if (shape.pace_tiles > 0 && pace_seq > 0) atomicAdd(shape.pace_counts + pace_seq - 1, 1u);
@@ -910,9 +998,6 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       static_assert(2 * TILE_N <= 256, "the merged hi|lo MMA needs 2 * TILE_N <= 256");
       const uint32_t idesc = make_idesc_tf32(kTileM, TILE_N, shape.a_mn != 0, shape.b_mn != 0);
       const uint32_t idesc_wide = make_idesc_tf32(kTileM, 2 * TILE_N, shape.a_mn != 0, shape.b_mn != 0);
-      // pair: M = 256 over both CTAs; each CTA's half of B is its own stage, so the three
-      // products are three MMAs of width TILE_N (64 cycles each at this width)
-      const uint32_t idesc_pair = make_idesc_tf32(2 * kTileM, TILE_N, shape.a_mn != 0, shape.b_mn != 0);
       const uint32_t a_lbo = shape.a_mn ? 4096u : 16u, a_sbo = shape.a_mn ? 512u : 1024u;
       const uint32_t b_lbo = shape.b_mn ? 4096u : 16u, b_sbo = shape.b_mn ? 512u : 1024u;
       const uint32_t a_kstep = shape.a_mn ? 1024u : 32u, b_kstep = shape.b_mn ? 1024u : 32u;
@@ -930,15 +1015,20 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
         return d;
       };
+      // pair: M = 256 over both CTAs; N counts the operand rows of both CTAs together
+      const uint32_t idesc_pair_wide = make_idesc_tf32(2 * kTileM, 2 * TILE_N, shape.a_mn != 0, shape.b_mn != 0);
+      const uint32_t idesc_pair_narrow = make_idesc_tf32(2 * kTileM, TILE_N, shape.a_mn != 0, shape.b_mn != 0);
       uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0, a_phase = 0;
       bool ok = true;
       FBMM_PROF_DECL;
+      FBMM_TRACE_DECL;
       for (long long u = unit_first; u < units && ok; u += unit_step) {
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range(b, mb, t0, t1, first, last)) continue;
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
+          FBMM_TRACE(0);
           FBMM_PROF_BEGIN();
           ok = wait_gate(&bars->acc_empty[acc_stage], acc_phase ^ 1u);
           FBMM_PROF_END(0);
@@ -949,7 +1039,9 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           for (int kb = 0; kb < kblocks; ++kb) {
             if (A_RES && t == first) {
               // 16-bit operands are used as they land; fp32 ones once their lo plane exists
+              FBMM_PROF_BEGIN();
               ok = wait_gate(kHalf ? &bars->a_full[kb] : &bars->a_split[kb], a_phase);
+              FBMM_PROF_END(3);
               if (!ok) break;
             }
             FBMM_PROF_BEGIN();
@@ -962,9 +1054,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t sb = smem_u32(ring + stage * plan.stage_bytes);
             const uint32_t sa = A_RES ? smem_u32(a_region + kb * kPlanes * kPlaneBytes) : sb;
             // Issue order: all four k-steps of one operand-plane combination before the
-            // next combination. Consecutive MMAs then walk the same 128-byte shared-memory
-            // rows, and the tensor core runs at its full rate (measured on pairs: 64 cycles
-            // per MMA, against 106 when the combinations alternate inside a k-step).
+            // next combination, so that consecutive MMAs walk the same 128-byte
+            // shared-memory rows.
             const uint32_t first_kb = kb == 0 ? 0u : 1u;
             const uint32_t a_hi0 = ((sa + off_a_hi) >> 4) | a_lbo_bits, a_lo0 = ((sa + off_a_lo) >> 4) | a_lbo_bits;
             const uint32_t b_hi0 = ((sb + off_b_hi) >> 4) | b_lbo_bits, b_lo0 = ((sb + off_b_lo) >> 4) | b_lbo_bits;
@@ -974,20 +1065,18 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int ks = 0; ks < 4; ++ks)  // big (+)= A * B, 16 elements of K per MMA
                 umma_f16(acc_big, pack(a_hi0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi),
                          idesc_half, ks == 0 ? first_kb : 1u);
-              (void)a_lo0; (void)b_lo0; (void)acc_small; (void)idesc; (void)idesc_wide; (void)idesc_pair;
+              (void)a_lo0; (void)b_lo0; (void)acc_small; (void)idesc; (void)idesc_wide;
             } else if (PAIR) {
+              const uint32_t b_nar0 = ((sb + off_b_narrow) >> 4) | b_lbo_bits;
 #pragma unroll
-              for (int ks = 0; ks < kKBlock / 8; ++ks)  // small (+)= A_lo * B_hi
-                umma_tf32_pair(acc_small, pack(a_lo0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi),
-                               idesc_pair, ks == 0 ? first_kb : 1u);
-#pragma unroll
-              for (int ks = 0; ks < kKBlock / 8; ++ks)  // small += A_hi * B_lo
-                umma_tf32_pair(acc_small, pack(a_hi0 + ks * a_step, a_desc_hi), pack(b_lo0 + ks * b_step, b_desc_hi),
-                               idesc_pair, 1u);
-#pragma unroll
-              for (int ks = 0; ks < kKBlock / 8; ++ks)  // big (+)= A_hi * B_hi
+              for (int ks = 0; ks < kKBlock / 8; ++ks)  // [big | small] (+)= A_hi * [B_hi (even CTA) | B_lo (odd CTA)]
                 umma_tf32_pair(acc_big, pack(a_hi0 + ks * a_step, a_desc_hi), pack(b_hi0 + ks * b_step, b_desc_hi),
-                               idesc_pair, ks == 0 ? first_kb : 1u);
+                               idesc_pair_wide, ks == 0 ? first_kb : 1u);
+#pragma unroll
+              for (int ks = 0; ks < kKBlock / 8; ++ks)  // small += A_lo * B_hi (64 columns from each CTA)
+                umma_tf32_pair(acc_small, pack(a_lo0 + ks * a_step, a_desc_hi), pack(b_nar0 + ks * b_step, b_desc_hi),
+                               idesc_pair_narrow, 1u);
+              (void)b_lo0;
             } else {
 #pragma unroll
               for (int ks = 0; ks < kKBlock / 8; ++ks)  // [big | small] (+)= A_hi * [B_hi | B_lo]
@@ -1035,7 +1124,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             uint8_t* ab = a_region + kb * 2 * kPlaneBytes;
             split_plane(ab + off_a_hi, ab + off_a_lo, kPlaneBytes, st);
             fence_proxy_async_smem();
-            arrive_leader(&bars->a_split[kb]);
+            warp_arrive_leader(&bars->a_split[kb]);
           }
           if (PRESPLIT) continue;
           FBMM_PROF_BEGIN();
@@ -1049,7 +1138,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           FBMM_PROF_END(1);
           FBMM_PROF_BEGIN();
           fence_proxy_async_smem();
-          arrive_leader(&bars->split[stage]);
+          warp_arrive_leader(&bars->split[stage]);
           FBMM_PROF_END(2);
           if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
@@ -1058,7 +1147,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     if (st == 0) { FBMM_PROF_FLUSH(8); }
     }
-  } else {
+  } else if (warp < 6u + epilogue_warps(EPI)) {
     // ------------------------------------------------------------------ epilogue
     const uint32_t quarter = warp & 3u;  // TMEM lanes this warp may read
     // 32-column chunks of a tile this warp handles
@@ -1067,9 +1156,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int chunk_end = chunk_first + kChunksPerWarp;
     const int row_in_tile = static_cast<int>(quarter * 32u + lane);
     const uint32_t lane_base = (quarter * 32u) << 16;
-    uint32_t acc_stage = 0, acc_phase = 0;
+    uint32_t acc_stage = 0, acc_phase = 0, mstage = 0, mphase = 0;
     bool ok = true;
     FBMM_PROF_DECL;
+    FBMM_TRACE_DECL;
 
     // 256-bit stores need every row start of C 32-byte aligned
     const bool c_lines_ok = (EPI == kEpiStore || EPI == kEpiMask) && ((epi.ldc & 7) == 0) &&
@@ -1116,9 +1206,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
       for (int t = t0; t < t1 && ok; ++t) {
         const int col_tile = t * TILE_N;
-        const bool any_live = tile_live(b, mb, t);      // loads and MMAs happen for this tile
-        const bool own_live = tile_live_own(b, mb, t);  // this CTA's 128x128 block keeps something
-        if (!own_live) {
+        const bool live = tile_live(b, mb, t);  // loads and MMAs happen for this tile
+        if (!live) {
           // masked-out block: the product is defined as zero (mbmm.py:74 pre-zeroes C).
           if (EPI == kEpiMask) {
             const int c_end = min(shape.N, col_tile + TILE_N);
@@ -1145,16 +1234,6 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int c = col_tile + chunk_first * 32; c < min(c_end, col_tile + chunk_end * 32); ++c) crow[c] = 0.f;
             }
           }
-        }
-        if (!any_live) continue;
-        if (!own_live) {
-          // the pair computed this tile for the peer's block: just hand the stage back
-          ok = mbar_wait(&bars->acc_full[acc_stage], acc_phase, abort_flag);
-          if (!ok) break;
-          tcgen05_fence_after_sync();
-          tcgen05_fence_before_sync();
-          arrive_leader(&bars->acc_empty[acc_stage]);
-          if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
           continue;
         }
         // Mask bytes of a 32-column chunk for this lane after the lane-quad transpose (lane q
@@ -1178,9 +1257,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                                                       static_cast<long long>(r) * shape.N + col0 + 8 * q);
           }
         };
-        if (mask_line_ok(col_tile + chunk_first * 32)) mask_fetch(col_tile + chunk_first * 32);
+        if (!mask_tma && mask_line_ok(col_tile + chunk_first * 32)) mask_fetch(col_tile + chunk_first * 32);
+        const uint8_t* mask_tile = epi_smem + mstage * kMaskStageBytes;
+        if (mask_tma) {
+            ok = mbar_wait(&bars->mask_full[mstage], mphase, abort_flag);
+            if (!ok) break;
+        }
         FBMM_PROF_BEGIN();
-        ok = mbar_wait(&bars->acc_full[acc_stage], acc_phase, abort_flag);
+        ok = wait_gate(&bars->acc_full[acc_stage], acc_phase);
         FBMM_PROF_END(0);
         if (!ok) break;
         tcgen05_fence_after_sync();
@@ -1192,7 +1276,18 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint32_t rb[32], rs[32];
           unsigned char tmv[4];
           uint2 e8[4];
-          if (EPI == kEpiMask) {
+          if (EPI == kEpiMask && mask_tma) {
+            // lane q of a quad: columns [8q, 8q + 8) of the quad's four rows, which share one
+            // 8-row thread-mask tile
+            const int q = static_cast<int>(lane & 3u);
+            const int row_l = static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
+            const unsigned char tb = mask_tile[kMaskElemBytes + (row_l >> 3) * 16 + c * 4 + q];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              tmv[i] = tb;
+              e8[i] = *reinterpret_cast<const uint2*>(mask_tile + (row_l + i) * 128 + c * 32 + 8 * q);
+            }
+          } else if (EPI == kEpiMask) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) { tmv[i] = tmv_n[i]; e8[i] = e8_n[i]; }
             if (c + 1 < chunk_end && mask_line_ok(col_tile + (c + 1) * 32)) mask_fetch(col_tile + (c + 1) * 32);
@@ -1205,8 +1300,13 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           FBMM_PROF_XBEGIN();
           if (c == chunk_end - 1) {
             // both accumulators of this stage are now in registers: hand the stage back
+            FBMM_PROF_XEND(1);
+            FBMM_PROF_XBEGIN();
             tcgen05_fence_before_sync();
-            arrive_leader(&bars->acc_empty[acc_stage]);
+            warp_arrive_leader(&bars->acc_empty[acc_stage]);
+            if (mask_tma) warp_arrive(&bars->mask_empty[mstage]);  // its mask bytes too
+            FBMM_PROF_XEND(2);
+            FBMM_PROF_XBEGIN();
           }
           float v[32];
 #pragma unroll
@@ -1391,7 +1491,9 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           FBMM_PROF_XEND(1);
         }
         FBMM_PROF_END(1);
+        if (threadIdx.x == 192) { FBMM_TRACE(1); }
         if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
+        if (mask_tma && ++mstage == kMaskStages) { mstage = 0; mphase ^= 1u; }
       }
 
       // ---- unit end
@@ -1414,6 +1516,29 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
     if (threadIdx.x == 6 * 32) { FBMM_PROF_FLUSH(12); FBMM_PROF_XFLUSH(); }
+  } else {
+    // ------------------------------------------------------------------ resident A loader
+    if (A_RES && lane == 0) {
+      uint32_t a_phase = 0;
+      bool ok = true;
+      for (long long u = unit_first; u < units && ok; u += unit_step) {
+        int b, mb, t0, t1, first, last;
+        decode(u, b, mb, t0, t1);
+        if (!live_range(b, mb, t0, t1, first, last)) continue;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          // free as soon as the previous unit's last tile has finished with that k-block
+          ok = wait_gate(&bars->a_empty[kb], a_phase ^ 1u);
+          if (!ok) break;
+          mbar_arrive_expect_tx(&bars->a_full[kb], kPlaneBytes);
+          load_a(&tmap_a, a_region + kb * kPlanes * kPlaneBytes + off_a_hi, &bars->a_full[kb], false, kb, mb, b);
+        }
+        a_phase ^= 1u;
+      }
+      if (!ok) {
+        const long long t0c = clock64();
+        while (clock64() - t0c < 2000000LL) {}
+      }
+    }
   }
 
   // ------------------------------------------------------------------ teardown

@@ -51,6 +51,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// One non-blocking test of an mbarrier phase (try_wait may suspend the thread for a while;
+// this never does).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred P;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, P;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Cycle budget of one wait (about two seconds at B200 clocks).
 constexpr long long kWaitBudgetCycles = 4000000000LL;
 
@@ -235,8 +251,8 @@ __device__ __forceinline__ void tmem_ld_wait() {
 
 // ----------------------------------------------------------------------------------
 // CTA pairs (clusters of two): cta_group::2 forms. The even-ranked CTA of a pair issues the
-// MMAs; each CTA supplies its own 128 rows of A and its own half of the B tile from its own
-// shared memory and owns the matching half of the accumulator in its own TMEM.
+// MMAs; each CTA supplies its own 128 rows of A and its own half of the MMA's N operand rows
+// from its own shared memory and owns its 128 accumulator rows in its own TMEM.
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
@@ -258,27 +274,31 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// Bounded wait on a local mbarrier whose arrivals come in through the cluster (the peer CTA's
+// arrive, a pair commit, the peer's copies): cluster-scope acquire, and an explicit, short
+// suspend-time limit on every poll (measured: polling in a tight loop instead takes issue
+// slots from the MMA thread and costs about 4 %).
+constexpr uint32_t kPairSuspendHintNs = 40;
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n"
       ".reg .pred P;\n"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2;\n"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 P, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, P;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kPairSuspendHintNs)
       : "memory");
   return ok != 0;
 }
-// Bounded wait on a local mbarrier whose arrivals may come from the peer CTA.
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {
   if (mbar_try_wait_cluster(bar, parity)) return true;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((++spins & 0x3ffu) == 0) {
+    if ((++spins & 0xffu) == 0) {
       if (*abort_flag != 0) return false;
       if (clock64() - t0 > kWaitBudgetCycles) {
         *abort_flag = 1;
@@ -323,7 +343,8 @@ __device__ __forceinline__ void umma_tf32_pair(uint32_t d_tmem, uint64_t a_desc,
       : "memory");
 }
 // Arrives on the mbarrier at `bar_cluster_addr` (either CTA of the pair) once every pair
-// MMA issued so far by this thread has completed.
+// MMA issued so far by this thread has completed. Measured: two of these in a row (one per
+// CTA) cost the issuing thread nothing next to the MMAs themselves.
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
                : "memory");
