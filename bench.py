@@ -614,6 +614,43 @@ def measure(name, args, rank, local_rank, world, dev, headline):
     return rec
 
 
+def measure_softmax_consumer(args, dev):
+    """The consumer behind mbmm (row softmax over the kept entries, scores never written) on
+    configuration 3's operands and masks: device-timed steps with an L2 flush in between, and
+    a check of three batches against the fp64 oracle. One GPU only (an extra, not a headline)."""
+    from custom_matmul_kernels_b200 import MBMMSoftmaxCUDA, make_masks
+    from oracle import ref_semantics as R
+    h = host_inputs("c3", 0, 1)
+    A, B = h["A"].to(dev), h["B"].to(dev)
+    masks = make_masks(h["mask"].to(dev))
+    op = MBMMSoftmaxCUDA()
+    scale = 0.125
+    flush = torch.zeros(L2_BYTES * 2 // 4, device=dev)
+    steps = max(args.steps, 30)
+    for _ in range(max(args.warmup, 3)):
+        P = op(A, B, *masks, scale=scale)
+    ms = timed_steps(lambda: op(A, B, *masks, scale=scale), steps, flush)
+    P = op(A, B, *masks, scale=scale)
+    worst, bad = 0.0, 0
+    for b in (0, 64, 127):
+        want = R.mbmm_softmax(h["A"][b], h["B"][b], *(t[b].cpu() for t in masks), scale=scale)
+        err = (P[b].cpu().double() - want).abs()
+        worst = max(worst, float(err.max()))
+        bad += int((err > 2e-6 + 1e-4 * want.abs()).sum()) + int((P[b].cpu()[~h["mask"][b]] != 0).sum())
+    l, m, k, n = SHAPES["c3"]
+    nbytes = algorithmic_bytes("c3", l, n) + l * m * n  # + the element mask, which this op reads in full
+    mean = statistics.mean(ms)
+    peaks = load_peaks()
+    del A, B, masks, P, flush
+    torch.cuda.empty_cache()
+    return {"op": "mbmm + row softmax (MBMMSoftmaxCUDA) on the c3 operands and masks", "steps": steps,
+            "ms_per_step": mean, "ms_per_step_best": min(ms), "batches_per_s": l / (mean / 1e3),
+            "achieved_gbs": nbytes / (mean / 1e3) / 1e9, "hbm_frac": nbytes / (mean / 1e3) / 1e9 / peaks["hbm_gbs"],
+            "algorithmic_bytes": nbytes,
+            "check": {"max_abs_err": worst, "unexplained": bad, "ok": bad == 0,
+                      "tolerance": "abs 2e-6 + rel 1e-4 on the probabilities, 3 batches, fp64 oracle"}}
+
+
 def run_ours(args):
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
     torch.cuda.set_device(local_rank)
@@ -628,6 +665,9 @@ def run_ours(args):
         for other in sorted(SHAPES):
             if other != name:
                 per[other] = measure(other, args, rank, local_rank, world, dev, False)
+    consumers = None
+    if world == 1 and not args.no_per_config:
+        consumers = {"c3_softmax": measure_softmax_consumer(args, dev)}
     if rank == 0:
         line = {
             "metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world,
@@ -642,6 +682,9 @@ def run_ours(args):
         if per:
             line["per_config"] = per
             line["gpu_launches"] += sum(p["gpu_launches"] for p in per.values())
+        if consumers:
+            line["consumers"] = consumers
+            line["gpu_launches"] += consumers["c3_softmax"]["steps"]
         if args.rows is not None or args.batches is not None:
             line["reduced"] = True
         print(json.dumps(line), flush=True)

@@ -5,9 +5,9 @@ The four callable classes keep the names and call signatures of the reference's
 sm_100a kernels in ``libfbmm.so`` (see ``include/fbmm.h`` for the C ABI).
 """
 from .bmm import BMMCUDA
-from .mbmm import MBMMCUDA, make_masks
+from .mbmm import MBMMCUDA, MBMMSoftmaxCUDA, make_masks
 from .minbmm import MinBMMCUDA
 from .topkbmm import TopkBMMCUDA
 from .kmeans import KMeansCUDA
 
-__all__ = ["BMMCUDA", "MBMMCUDA", "MinBMMCUDA", "TopkBMMCUDA", "KMeansCUDA", "make_masks"]
+__all__ = ["BMMCUDA", "MBMMCUDA", "MBMMSoftmaxCUDA", "MinBMMCUDA", "TopkBMMCUDA", "KMeansCUDA", "make_masks"]

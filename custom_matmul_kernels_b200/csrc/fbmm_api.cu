@@ -93,6 +93,7 @@ int device_state(DeviceState** out) {
     int rc;
     if ((rc = set_smem_attr<kEpiStore, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiMask, 1>()) != FBMM_OK) return rc;
+    if ((rc = set_smem_attr<kEpiSoftmax, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiMin, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiTopk, 1>()) != FBMM_OK) return rc;
     if ((rc = set_smem_attr<kEpiTopk, 2>()) != FBMM_OK) return rc;
@@ -483,7 +484,7 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
   const bool a_resident = a_stays_resident(p.K);
   // mask tiles by TMA when the masks allow it (the kernel reads them from global memory otherwise)
   CUtensorMap tem = ta, ttm = ta;
-  if (EPI == kEpiMask && masks_fit_tma(epi, p.N)) {
+  if (is_masked(EPI) && masks_fit_tma(epi, p.N)) {
     if ((rc = make_mask_maps(&tem, &ttm, epi, p.L, p.M, p.N)) != FBMM_OK) return rc;
     epi_args.mask_tma = 1;
   }
@@ -618,6 +619,40 @@ int fbmm_mbmm_f32(void* stream, const float* A, int a_layout, long long lda, lon
   e.tm_stride = share_mask ? 0 : static_cast<long long>((m + 7) / 8) * e.tm_cols;
   e.em_stride = share_mask ? 0 : static_cast<long long>(m) * n;
   return launch_gemm<kEpiMask, 1>(static_cast<cudaStream_t>(stream), *st, p, s, e);
+}
+
+int fbmm_mbmm_softmax_f32(void* stream, const float* A, int a_layout, long long lda, long long stride_a, const float* B,
+                          int b_layout, long long ldb, long long stride_b, float* P, long long ldp, long long stride_p,
+                          const unsigned char* block_mask, const unsigned char* thread_mask,
+                          const unsigned char* element_mask, int share_mask, float scale, int l, int m, int n, int k) {
+  int rc;
+  if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
+  if (P == nullptr) return fail(FBMM_ERR_INVALID, "P is null");
+  if (ldp < n) return fail(FBMM_ERR_INVALID, "ldp %lld smaller than n %d", ldp, n);
+  if (block_mask == nullptr || thread_mask == nullptr || element_mask == nullptr)
+    return fail(FBMM_ERR_INVALID, "a mask pointer is null");
+  if (!(scale == scale) || scale == INFINITY || scale == -INFINITY) return fail(FBMM_ERR_INVALID, "scale must be finite");
+  RowProblem p;
+  if ((rc = make_row_problem(&p, A, a_layout, lda, stride_a, B, b_layout, ldb, stride_b, l, m, n, k, 2)) != FBMM_OK) return rc;
+  if ((rc = check_operand("A", p.a, k, l)) != FBMM_OK) return rc;
+  if ((rc = check_operand("B", p.b, k, l)) != FBMM_OK) return rc;
+  DeviceState* st;
+  if ((rc = device_state(&st)) != FBMM_OK) return rc;
+  GemmShape s = base_shape(p);
+  // one CTA owns whole rows: the row's maximum and sum live in its registers across the sweep
+  s.n_chunks = 1;
+  s.tiles_per_chunk = s.n_tiles;
+  s.num_units = static_cast<long long>(l) * s.m_blocks;
+  EpiArgs e{};
+  e.C = P; e.ldc = ldp; e.stride_c = stride_p;
+  e.block_mask = block_mask; e.thread_mask = thread_mask; e.element_mask = element_mask;
+  e.bm_cols = (n + 127) / 128;
+  e.tm_cols = (n + 7) / 8;
+  e.bm_stride = share_mask ? 0 : static_cast<long long>((m + 127) / 128) * e.bm_cols;
+  e.tm_stride = share_mask ? 0 : static_cast<long long>((m + 7) / 8) * e.tm_cols;
+  e.em_stride = share_mask ? 0 : static_cast<long long>(m) * n;
+  e.softmax_scale_log2e = scale * 1.4426950408889634f;
+  return launch_gemm<kEpiSoftmax, 1>(static_cast<cudaStream_t>(stream), *st, p, s, e);
 }
 
 size_t fbmm_min_bmm_workspace_bytes(int l, int m, int n, int k, int dim, int distance) {

@@ -45,7 +45,13 @@ constexpr int kSplitThreads = 128;
 constexpr int kTmemCols = 512;
 constexpr long long kPaceWaitCycles = 4000000;  // longest a CTA holds back for the others (~2 ms)
 
-enum EpilogueKind { kEpiStore = 0, kEpiMask = 1, kEpiMin = 2, kEpiTopk = 3 };
+enum EpilogueKind { kEpiStore = 0, kEpiMask = 1, kEpiMin = 2, kEpiTopk = 3, kEpiSoftmax = 4 };
+// epilogues that take the three masks of mbmm
+__host__ __device__ constexpr bool is_masked(int epi) { return epi == kEpiMask || epi == kEpiSoftmax; }
+// Row softmax over the kept entries of a masked product: the unit's column tiles are swept
+// twice (the row block of A stays in shared memory, B streams past again), first for the
+// row maxima and sums, then for the probabilities, so the scores never reach global memory.
+__host__ __device__ constexpr int sweeps(int epi) { return epi == kEpiSoftmax ? 2 : 1; }
 
 // Epilogue warps. A warp may read only the 32 TMEM lanes (rows) 32 * (warp % 4) onwards, so
 // four warps cover a tile. The mask epilogue runs two warps per row quarter, each on half of
@@ -150,6 +156,7 @@ struct EpiArgs {
   const unsigned char* element_mask;  // [L or 1][M][N]
   long long bm_stride, tm_stride, em_stride;  // per-batch strides, 0 when shared
   int bm_cols, tm_cols;
+  float softmax_scale_log2e;  // softmax epilogue: scale * log2(e), applied to the products before exp2
   int mask_tma;  // the element and thread masks of a tile come through shared memory by TMA (tensor maps
                  // tmap_em / tmap_tm are valid: n a multiple of 128, mask bases 16-byte aligned)
   // min
@@ -722,7 +729,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr int kKElems = kHalf ? 2 * kKBlock : kKBlock;  // elements of K per k-block (128 bytes)
   const int kblocks = (shape.K + kKElems - 1) / kKElems;
   constexpr uint32_t kPlanes = kHalf ? 1u : 2u;  // planes per operand tile in shared memory
-  const bool mask_tma = EPI == kEpiMask && epi.mask_tma != 0;
+  const bool mask_tma = is_masked(EPI) && epi.mask_tma != 0;
+  constexpr int kSweeps = sweeps(EPI);
   const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, kPlanes, mask_tma, PAIR);
   const uint32_t stages = plan.stages;
   constexpr uint32_t kBPlane = kPlaneBytes;  // one plane of a B tile
@@ -821,12 +829,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     return epi.block_mask[b * epi.bm_stride + static_cast<long long>(mb128) * epi.bm_cols + t] != 0;
   };
   auto tile_live = [&](int b, int mb, int t) -> bool {
-    if (EPI != kEpiMask) return true;
+    if (!is_masked(EPI)) return true;
     return block_live(b, mb, t);
   };
   // First and last live tile of a unit; false when the unit has none.
   auto live_range = [&](int b, int mb, int t0, int t1, int& first, int& last) -> bool {
-    if (EPI != kEpiMask) { first = t0; last = t1 - 1; return t0 < t1; }
+    if (!is_masked(EPI)) { first = t0; last = t1 - 1; return t0 < t1; }
     first = -1; last = -1;
     for (int t = t0; t < t1; ++t)
       if (tile_live(b, mb, t)) { if (first < 0) first = t; last = t; }
@@ -915,6 +923,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range(b, mb, t0, t1, first, last)) continue;
+        for (int sweep = 0; sweep < kSweeps; ++sweep)
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
           if (shape.pace_tiles > 0 && cta_rank == 0 && (t - t0) % shape.pace_tiles == 0) {
@@ -1026,6 +1035,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range(b, mb, t0, t1, first, last)) continue;
+        for (int sweep = 0; sweep < kSweeps; ++sweep)
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
           FBMM_TRACE(0);
@@ -1037,7 +1047,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t acc_big = tmem_base + acc_stage * (2 * TILE_N);
           const uint32_t acc_small = acc_big + TILE_N;
           for (int kb = 0; kb < kblocks; ++kb) {
-            if (A_RES && t == first) {
+            if (A_RES && t == first && sweep == 0) {
               // 16-bit operands are used as they land; fp32 ones once their lo plane exists
               FBMM_PROF_BEGIN();
               ok = wait_gate(kHalf ? &bars->a_full[kb] : &bars->a_split[kb], a_phase);
@@ -1089,7 +1099,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               (void)b_lo0;
             }
             commit_all(&bars->empty[stage]);
-            if (A_RES && t == last) commit_all(&bars->a_empty[kb]);
+            if (A_RES && t == last && sweep == kSweeps - 1) commit_all(&bars->a_empty[kb]);
             FBMM_PROF_END(2);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
@@ -1114,11 +1124,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int b, mb, t0, t1, first, last;
       decode(u, b, mb, t0, t1);
       if (!live_range(b, mb, t0, t1, first, last)) continue;
+      for (int sweep = 0; sweep < kSweeps; ++sweep)
       for (int t = first; t <= last && ok; ++t) {
         if (!tile_live(b, mb, t)) continue;
-        if (PRESPLIT && t != first) break;  // only the unit's resident A block needs splitting
+        if (PRESPLIT && (t != first || sweep != 0)) break;  // only the unit's resident A block needs splitting
         for (int kb = 0; kb < kblocks; ++kb) {
-          if (A_RES && t == first) {
+          if (A_RES && t == first && sweep == 0) {
             ok = mbar_wait(&bars->a_full[kb], a_phase, abort_flag);
             if (!ok) break;
             uint8_t* ab = a_region + kb * 2 * kPlaneBytes;
@@ -1162,7 +1173,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     FBMM_TRACE_DECL;
 
     // 256-bit stores need every row start of C 32-byte aligned
-    const bool c_lines_ok = (EPI == kEpiStore || EPI == kEpiMask) && ((epi.ldc & 7) == 0) &&
+    const bool c_lines_ok = (EPI == kEpiStore || is_masked(EPI)) && ((epi.ldc & 7) == 0) &&
                             ((epi.stride_c & 7) == 0) && ((reinterpret_cast<uintptr_t>(epi.C) & 31) == 0);
     // 8-byte reads of the element mask need its rows 8-byte aligned
     const bool em_lines_ok = (EPI == kEpiMask) && ((shape.N & 7) == 0) && ((epi.em_stride & 7) == 0) &&
@@ -1204,12 +1215,17 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         si = reinterpret_cast<int*>(sv + kListEntries);
       }
 
+      // softmax: running maximum (in the exp2 domain) and sum of this row over the kept entries
+      float sm_max = -INFINITY, sm_sum = 0.f, sm_inv = 0.f;
+
+      for (int sweep = 0; sweep < kSweeps; ++sweep) {
+      if (EPI == kEpiSoftmax && sweep == 1) sm_inv = sm_sum > 0.f ? 1.f / sm_sum : 0.f;
       for (int t = t0; t < t1 && ok; ++t) {
         const int col_tile = t * TILE_N;
         const bool live = tile_live(b, mb, t);  // loads and MMAs happen for this tile
         if (!live) {
           // masked-out block: the product is defined as zero (mbmm.py:74 pre-zeroes C).
-          if (EPI == kEpiMask) {
+          if (EPI == kEpiMask || (EPI == kEpiSoftmax && sweep == 1)) {
             const int c_end = min(shape.N, col_tile + TILE_N);
             if (kHalf) {
               // 16-bit C: element-wise zeros over this warp's columns of the row
@@ -1276,6 +1292,35 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint32_t rb[32], rs[32];
           unsigned char tmv[4];
           uint2 e8[4];
+          // softmax: bit j set when column j of this thread's row in the chunk survives all three
+          // masks (a zero thread-mask byte drops its 8 x 8 tile, a zero element byte the entry;
+          // columns past N never count). Read before the TMEM loads: after the last chunk's
+          // loads the mask stage goes back to the producer.
+          uint32_t keep = 0;
+          if (EPI == kEpiSoftmax) {
+            const int kc0 = col_tile + c * 32;
+            if (mask_tma) {
+              const uint4 e0 = *reinterpret_cast<const uint4*>(mask_tile + row_in_tile * 128 + c * 32);
+              const uint4 e1 = *reinterpret_cast<const uint4*>(mask_tile + row_in_tile * 128 + c * 32 + 16);
+              const uint32_t tmw =
+                  *reinterpret_cast<const uint32_t*>(mask_tile + kMaskElemBytes + (row_in_tile >> 3) * 16 + c * 4);
+              const uint32_t ew[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const uint32_t eb = (ew[j >> 2] >> ((j & 3) * 8)) & 0xffu, tb = (tmw >> ((j >> 3) * 8)) & 0xffu;
+                keep |= ((eb != 0u && tb != 0u) ? 1u : 0u) << j;
+              }
+            } else if (row_ok) {
+              const unsigned char* tm =
+                  epi.thread_mask + b * epi.tm_stride + static_cast<long long>(row >> 3) * epi.tm_cols + (kc0 >> 3);
+              const unsigned char* em = epi.element_mask + b * epi.em_stride + static_cast<long long>(row) * shape.N + kc0;
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (kc0 + j < shape.N && tm[j >> 3] != 0 && em[j] != 0) keep |= 1u << j;
+            }
+            if (kc0 + 32 > shape.N) keep &= (kc0 < shape.N) ? ((1u << (shape.N - kc0)) - 1u) : 0u;
+            if (!row_ok) keep = 0;
+          }
           if (EPI == kEpiMask && mask_tma) {
             // lane q of a quad: columns [8q, 8q + 8) of the quad's four rows, which share one
             // 8-row thread-mask tile
@@ -1412,6 +1457,47 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                   if (col0 + j < shape.N) crow[j] = v[j];
               }
             }
+          } else if (EPI == kEpiSoftmax) {
+            // This thread's row, 32 columns; scores go to the exp2 domain: s = (a.b) * scale * log2(e).
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= epi.softmax_scale_log2e;
+            if (sweep == 0) {
+              float cmax = -INFINITY;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) cmax = ((keep >> j) & 1u) ? fmaxf(cmax, v[j]) : cmax;
+              if (cmax > sm_max) {  // (never true for a chunk that keeps nothing)
+                sm_sum *= exp2f(sm_max - cmax);  // exp2(-inf) = 0 on the first kept chunk
+                sm_max = cmax;
+              }
+              if (keep != 0u) {
+                float part = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) part += ((keep >> j) & 1u) ? exp2f(v[j] - sm_max) : 0.f;
+                sm_sum += part;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = ((keep >> j) & 1u) ? exp2f(v[j] - sm_max) * sm_inv : 0.f;
+              const bool line_path = c_lines_ok && col0 + 32 <= shape.N;
+              if (line_path) {
+                // whole warp: after the transpose lane q of a lane quad holds columns [8q, 8q + 8)
+                // of the quad's four rows, and every store instruction writes eight whole lines
+                transpose_rows_in_lane_quads(v);
+                const int q = static_cast<int>(lane & 3u);
+                const int row_g = row_base(mb) + static_cast<int>(quarter) * 32 + static_cast<int>(lane & ~3u);
+                float* cbase = epi.C + b * epi.stride_c + static_cast<long long>(row_g) * epi.ldc + col0 + 8 * q;
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                  if (row_g + i < shape.M)
+                    st_global_v8_streaming(cbase + static_cast<long long>(i) * epi.ldc, v[8 * i], v[8 * i + 1], v[8 * i + 2],
+                                           v[8 * i + 3], v[8 * i + 4], v[8 * i + 5], v[8 * i + 6], v[8 * i + 7]);
+              } else if (row_ok && col0 < shape.N) {
+                float* crow = epi.C + b * epi.stride_c + static_cast<long long>(row) * epi.ldc + col0;
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                  if (col0 + j < shape.N) crow[j] = v[j];
+              }
+            }
           } else if (EPI == kEpiMin) {
             // kernels/minbmm.cu:86-153 keeps the first index under a strict '<'. Here: the
             // chunk minimum by a comparison tree, then -- only when it beats the running
@@ -1495,6 +1581,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
         if (mask_tma && ++mstage == kMaskStages) { mstage = 0; mphase ^= 1u; }
       }
+      }  // sweeps
 
       // ---- unit end
       if (EPI == kEpiMin) {

@@ -57,6 +57,8 @@ SIGNATURES = {
     "fbmm_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ll, _c_ll, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_mbmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int,
                                                       _c_int, _c_int, _c_int, _c_int]),
+    "fbmm_mbmm_softmax_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ll, _c_ll, _c_ptr, _c_ptr, _c_ptr, _c_int,
+                                                              ctypes.c_float, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_min_bmm_workspace_bytes": (_c_size, [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int]),
     "fbmm_min_bmm_f32": (_c_int, [_c_ptr] + _OPERANDS + [_c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                                                          _c_int, _c_ptr, _c_size]),

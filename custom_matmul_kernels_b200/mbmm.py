@@ -116,3 +116,47 @@ class MBMMCUDA(CustomKernel):
         else:
             raise ValueError(f"unknown mode {mode!r}")
         return C[0] if two_d else C
+
+
+class MBMMSoftmaxCUDA(MBMMCUDA):
+    """``MBMMSoftmaxCUDA(share_mask=False)(A, B, block_mask, thread_mask, element_mask, scale=1.0) -> P``:
+    the masked product followed by a softmax over the kept entries of every row,
+    ``softmax(scale * (A @ B) with masked entries at -inf, dim=-1)``, without the scores
+    ever being written out. This is the step that callers of the reference's masked bmm
+    (mbmm.py:109-196) run next when the mask is an attention mask; the reference itself has
+    no such op. Masked entries are 0 in P, and a row that keeps nothing is all zeros (torch
+    gives NaN there). Masks as for MBMMCUDA, read as keep (non-zero) / drop; fp32 only."""
+
+    def __call__(self, A, B, block_mask, thread_mask, element_mask, scale=1.0):
+        A3, B3, two_d = self.check_inputs(A, B, (torch.float32,))
+        if two_d and not self.share_mask:
+            block_mask, thread_mask, element_mask = block_mask[None], thread_mask[None], element_mask[None]
+        l, m, k = A3.shape
+        n = B3.shape[2]
+        lead = () if self.share_mask else (l,)
+        want = {"block_mask": lead + (math.ceil(m / 128), math.ceil(n / 128)),
+                "thread_mask": lead + (math.ceil(m / 8), math.ceil(n / 8)), "element_mask": lead + (m, n)}
+        got = {"block_mask": block_mask, "thread_mask": thread_mask, "element_mask": element_mask}
+        for name, shape in want.items():
+            if got[name].dtype != torch.uint8:
+                raise TypeError(f"{name} must be uint8")
+            if got[name].device != A3.device:
+                raise ValueError(f"{name} must be on the same device as A")
+            if tuple(got[name].shape) != shape:
+                raise ValueError(f"{name} has shape {tuple(got[name].shape)}, expected {shape}")
+        P = torch.empty((l, m, n), device=A3.device, dtype=torch.float32)
+        if l == 0 or m == 0 or n == 0:
+            return P[0] if two_d else P
+        if k == 0:
+            raise ValueError("k must be positive")
+        bm, tm, em = block_mask.contiguous(), thread_mask.contiguous(), element_mask.contiguous()
+        a_keep, a_t, lda, sa = operand(A3)
+        b_keep, b_t, ldb, sb = operand(B3)
+        with torch.cuda.device(A3.device):
+            check(self.lib.fbmm_mbmm_softmax_f32(
+                self.stream_ptr(A3.device),
+                a_keep.data_ptr(), layout_letter(a_t, False), lda, sa,
+                b_keep.data_ptr(), layout_letter(b_t, True), ldb, sb,
+                P.data_ptr(), n, m * n, bm.data_ptr(), tm.data_ptr(), em.data_ptr(), 1 if self.share_mask else 0,
+                float(scale), l, m, n, k))
+        return P[0] if two_d else P

@@ -93,6 +93,24 @@ int fbmm_mbmm_f32(void* stream,
                   const unsigned char* element_mask, int share_mask,
                   int l, int m, int n, int k);
 
+/* Masked row softmax on top of mbmm, the consumer that attention-style callers put behind the
+ * masked product: P[l,m,n] = softmax over the KEPT entries of each row of scale * (A @ B),
+ * 0 where an entry is masked out (masks as for fbmm_mbmm_f32, read as keep / drop: any
+ * non-zero element byte keeps), and an all-zero row where nothing is kept. The scores never
+ * reach global memory: a CTA owns 128 whole rows, sweeps their column tiles once for the row
+ * maxima and sums and a second time (B streams past again, A stays in shared memory) for the
+ * probabilities, which is all it writes. Tiles whose block-mask byte is 0 are skipped in both
+ * sweeps. The reference stops at the masked product (mbmm.py:109-196, kernels/mbmm.cu:209-374);
+ * its notebook's comparison expression with the softmax applied,
+ * torch.softmax(torch.bmm(A, B).masked_fill(~mask, -inf) * scale, -1), is the oracle. */
+int fbmm_mbmm_softmax_f32(void* stream,
+                          const float* A, int a_layout, long long lda, long long stride_a,
+                          const float* B, int b_layout, long long ldb, long long stride_b,
+                          float* P, long long ldp, long long stride_p,
+                          const unsigned char* block_mask, const unsigned char* thread_mask,
+                          const unsigned char* element_mask, int share_mask, float scale,
+                          int l, int m, int n, int k);
+
 /* Row-wise (dim = 2, output [l, m]) or column-wise (dim = 1, output [l, n]) minimum and
  * argmin of A @ B without materialising the product. Replaces min_bmm_nn/nt/tn/tt
  * (kernels/minbmm.cu:348,252,156,443) with their epilogues min_dim_2 / min_dim_1

@@ -112,6 +112,25 @@ def mbmm(A, B, block_mask, thread_mask, element_mask, share_mask=False, dtype=to
     return C[0] if two_d else C
 
 
+def mbmm_softmax(A, B, block_mask, thread_mask, element_mask, share_mask=False, scale=1.0, dtype=torch.float64):
+    """Softmax over the kept entries of each row of scale * (A @ B): the masked product of
+    colab/test_mbmm.ipynb:1342-1343 with -inf instead of 0 at the masked entries, then
+    torch.softmax along the last axis. Rows that keep nothing are all zeros. The keep set is
+    the one the three masks define together (kernels/mbmm.cu:251-255,360-363,111-133)."""
+    A3, B3, two_d = _as3d(A, B)
+    l, m, _ = A3.shape
+    n = B3.shape[2]
+    bm, tm, em = (x[None] if x.dim() == 2 else x for x in (block_mask, thread_mask, element_mask))
+    tiles, em = effective_keep(bm, tm, em, m, n)
+    keep = (tiles & (em != 0)).expand(l, m, n)
+    S = torch.bmm(A3.to(dtype), B3.to(dtype)) * scale
+    S = S.masked_fill(~keep, float("-inf"))
+    P = torch.softmax(S, dim=-1)
+    P = torch.where(keep, P, torch.zeros_like(P))
+    P = torch.nan_to_num(P, nan=0.0)
+    return P[0] if two_d else P
+
+
 def product(A3, B3, distance="inner", dtype=torch.float32):
     """The [l,m,n] matrix the epilogues reduce: the products (madd,
     kernels/bmm_helpers.cu:20-26) or, for distance "l2"/"euclidean", the squared distances

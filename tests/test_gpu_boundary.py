@@ -137,3 +137,49 @@ def test_tensor_map_cache_returns_the_same_answers(dev, lib):
         X = torch.randn(1, 128, 32, generator=g).to(dev)
         assert tol_ratio(op(X, X.transpose(1, 2).contiguous()), R.bmm(X.cpu(), X.cpu().transpose(1, 2), dtype=torch.float64)) <= 1.0
     assert torch.equal(op(A, B), C1)
+
+
+def test_masked_row_softmax_matches_the_oracle(dev, lib):
+    """softmax(scale * A @ B with masked entries at -inf) against the fp64 oracle: causal and
+    random-tile masks of configuration 3's kind (mask tiles through TMA), a ragged shape with
+    an all-masked block and empty rows (masks read from global memory), shared masks.
+    Tolerance: abs 2e-6 + rel 1e-4 on the probabilities (fp32 scores are good to 1e-5 rel /
+    1e-4 abs, which the exponential turns into a relative error of that size)."""
+    from custom_matmul_kernels_b200 import MBMMSoftmaxCUDA, make_masks
+
+    def check(P, want, mask):
+        P, want = P.cpu().double(), want.double()
+        assert bool((P[~mask] == 0).all()), "a masked entry is not exactly zero"
+        err = (P - want).abs()
+        assert bool((err <= 2e-6 + 1e-4 * want.abs()).all()), float(err.max())
+        rows_kept = mask.any(dim=-1)
+        assert bool(((P.sum(-1) - 1).abs()[rows_kept] < 1e-4).all()) and bool((P.sum(-1)[~rows_kept] == 0).all())
+
+    g = torch.Generator().manual_seed(31)
+    # configuration-3-like: multiples of 128, causal + 64x64 random tiles
+    l, m, k, n = 4, 1024, 64, 1024
+    A, B = torch.randn(l, m, k, generator=g), torch.randn(l, k, n, generator=g)
+    mask = torch.zeros(l, m, n, dtype=torch.bool)
+    mask[:2] = torch.tril(torch.ones(m, n, dtype=torch.bool))
+    tiles = torch.rand(2, m // 64, n // 64, generator=g) < 0.3
+    mask[2:] = tiles.repeat_interleave(64, 1).repeat_interleave(64, 2)
+    bm, tm, em = make_masks(mask.to(dev))
+    scale = 1.0 / 8.0
+    P = MBMMSoftmaxCUDA()(A.to(dev), B.to(dev), bm, tm, em, scale=scale)
+    check(P, R.mbmm_softmax(A, B, bm.cpu(), tm.cpu(), em.cpu(), scale=scale), mask)
+    assert torch.equal(P, MBMMSoftmaxCUDA()(A.to(dev), B.to(dev), bm, tm, em, scale=scale))  # deterministic
+    # ragged, k > 128 (A streams), a dead block, rows that keep nothing
+    l, m, k, n = 2, 200, 160, 300
+    A, B = torch.randn(l, m, k, generator=g), torch.randn(l, k, n, generator=g)
+    mask = torch.rand(l, m, n, generator=g) < 0.4
+    mask[:, :128, 128:256] = False
+    mask[0, 7] = False
+    mask[1, 150:] = False
+    bm, tm, em = make_masks(mask.to(dev))
+    P = MBMMSoftmaxCUDA()(A.to(dev), B.to(dev), bm, tm, em, scale=0.5)
+    check(P, R.mbmm_softmax(A, B, bm.cpu(), tm.cpu(), em.cpu(), scale=0.5), mask)
+    # shared masks, 2-D inputs
+    bm1, tm1, em1 = make_masks(mask[0].to(dev))
+    P1 = MBMMSoftmaxCUDA(share_mask=True)(A[0].to(dev), B[0].to(dev), bm1, tm1, em1, scale=0.5)
+    assert torch.equal(P1, P[0])
+    assert lib.fbmm_check(None) == 0
