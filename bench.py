@@ -413,21 +413,30 @@ def algorithmic_bytes(name, units, n_cols):
     return units * k * 4 + k * n_cols * 4 + units * TOPK * 12
 
 
-def measured_traffic(name, units):
-    """DRAM bytes per launch from the ncu captures summarised in profiles/, scaled by the units
-    processed; None where no capture has been taken.
-    c4 (min kernel at 262 144 rows: 352.3 MB read + 5.4 MB written): B's hi and lo planes
-    (67.1 MB) are read once per launch whatever the row count; the rest (A, read once per
-    column range = twice, and the outputs) grows with the rows."""
-    if name == "c4":
-        b_planes = 2 * 128 * 65536 * 4
-        per_row = (352.28288e6 + 5.39648e6 - b_planes) / 262144.0
-        return b_planes + units * per_row
-    return TRAFFIC_PER_UNIT.get(name, lambda u: None)(units)
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of ONE launch of the fused kernel, from
+# the ncu captures summarised in profiles/: (units captured, bytes that do not grow with the
+# units, bytes that do).
+#   c1-c3: the full workload was captured; everything is scaled by the rows / batches.
+#   c4: 262 144 rows; B's hi and lo planes (67.1 MB) are read once per launch, the rest (A, once
+#       per column range, and the keys) grows with the rows.
+#   c5: 37 888 rows = two waves of 74 CTA pairs; every wave streams B's planes (2 x 1 GiB) from
+#       DRAM once, so the traffic grows with the number of waves: bytes per row = capture / rows.
+TRAFFIC_CAPTURES = {
+    "c1": (16384, 0.0, 12766464.0 + 0.0),
+    "c2": (128, 0.0, 142640640.0 + 477262080.0),
+    "c3": (128, 0.0, 202073344.0 + 478761728.0),
+    "c4": (262144, 2.0 * 128 * 65536 * 4, 356611840.0 + 5492992.0 - 2.0 * 128 * 65536 * 4),
+    "c5": (37888, 0.0, 4635089152.0 + 292627200.0),
+}
 
 
-# per-launch DRAM traffic of the c2 / c3 kernels from the captures in profiles/ (bytes per batch)
-TRAFFIC_PER_UNIT = {}
+def measured_traffic(name, units, n_cols):
+    """DRAM bytes per launch of the fused kernel, scaled from the capture by the units this rank
+    processes; None for a column shard (no capture of that shape was taken)."""
+    if n_cols != SHAPES[name][3]:
+        return None
+    cap_units, fixed, growing = TRAFFIC_CAPTURES[name]
+    return fixed + growing * units / cap_units
 
 
 def cpu_baseline(name, budget_s):
@@ -514,7 +523,7 @@ def roofline(name, wl, ms_mean, peaks, world):
                       "frac_sustained": achieved_tflops / sustained, "frac_mma_issue_ceiling": achieved_tflops / 341.0}
     roof["hbm"] = {"achieved_gbs": achieved_gbs, "frac": achieved_gbs / peaks["hbm_gbs"], "algorithmic_bytes": nbytes}
     roof["ideal_ms"] = {"tensor_burst": tensor_time * 1e3, "hbm": hbm_time * 1e3}
-    roof["traffic"] = measured_traffic(name, units)
+    roof["traffic"] = measured_traffic(name, units, n_cols)
     roof["kernel"] = "fbmm_gemm_kernel"
     return roof
 
@@ -626,13 +635,25 @@ def measure_softmax_consumer(args, dev):
     op = MBMMSoftmaxCUDA()
     scale = 0.125
     flush = torch.zeros(L2_BYTES * 2 // 4, device=dev)
-    steps = max(args.steps, 30)
+    steps = args.steps if args.consumer_only else max(args.steps, 30)
     for _ in range(max(args.warmup, 3)):
         P = op(A, B, *masks, scale=scale)
     ms = timed_steps(lambda: op(A, B, *masks, scale=scale), steps, flush)
     P = op(A, B, *masks, scale=scale)
+    # the same result from separate steps: the masked product written out by MBMMCUDA, then
+    # torch's where + softmax over it (what a caller of the reference's mbmm would run next)
+    from custom_matmul_kernels_b200 import MBMMCUDA
+    mbmm, keep = MBMMCUDA(), h["mask"].to(dev)
+    neg = torch.full((), float("-inf"), device=dev)
+
+    def unfused():
+        return torch.softmax(torch.where(keep, mbmm(A, B, *masks) * scale, neg), dim=-1)
+    for _ in range(3):
+        unfused()
+    ms_unfused = timed_steps(unfused, min(steps, 10), flush)
+    del keep
     worst, bad = 0.0, 0
-    for b in (0, 64, 127):
+    for b in sorted({0, SHAPES["c3"][0] // 2, SHAPES["c3"][0] - 1}):
         want = R.mbmm_softmax(h["A"][b], h["B"][b], *(t[b].cpu() for t in masks), scale=scale)
         err = (P[b].cpu().double() - want).abs()
         worst = max(worst, float(err.max()))
@@ -645,6 +666,8 @@ def measure_softmax_consumer(args, dev):
     torch.cuda.empty_cache()
     return {"op": "mbmm + row softmax (MBMMSoftmaxCUDA) on the c3 operands and masks", "steps": steps,
             "ms_per_step": mean, "ms_per_step_best": min(ms), "batches_per_s": l / (mean / 1e3),
+            "ms_per_step_unfused": statistics.mean(ms_unfused),
+            "unfused": "MBMMCUDA, then torch.where(mask, C * scale, -inf) and torch.softmax",
             "achieved_gbs": nbytes / (mean / 1e3) / 1e9, "hbm_frac": nbytes / (mean / 1e3) / 1e9 / peaks["hbm_gbs"],
             "algorithmic_bytes": nbytes,
             "check": {"max_abs_err": worst, "unexplained": bad, "ok": bad == 0,
@@ -757,6 +780,9 @@ def main():
     ap.add_argument("--batches", type=int, default=None,
                     help="profiling only: cut c2/c3 to this many batches (the line is marked reduced)")
     ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the end-to-end legs")
+    ap.add_argument("--consumer-only", action="store_true",
+                    help="profiling only: run just the masked row softmax on the c3 operands (honours --batches) "
+                         "and print its record")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = {"c1": 50, "c2": 30, "c3": 30, "c4": 10, "c5": 4}[args.workload]
@@ -768,6 +794,10 @@ def main():
         SHAPES[args.workload] = (args.batches, m, k, n)
     if args.rows is not None or args.batches is not None:
         args.no_per_config = True
+    if args.consumer_only:
+        torch.cuda.set_device(0)
+        print(json.dumps({"consumers": {"c3_softmax": measure_softmax_consumer(args, torch.device("cuda", 0))}}))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

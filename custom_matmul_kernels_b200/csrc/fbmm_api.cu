@@ -488,7 +488,7 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
     if ((rc = make_mask_maps(&tem, &ttm, epi, p.L, p.M, p.N)) != FBMM_OK) return rc;
     epi_args.mask_tma = 1;
   }
-  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, 2u, epi_args.mask_tma != 0, pairs);
+  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, 2u, epi_args.mask_tma != 0, pairs, EPI == kEpiSoftmax);
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
   // min / top-k have pre-split variants; store / mask never use them
   constexpr bool kHasPresplit = (EPI == kEpiMin || EPI == kEpiTopk);

@@ -58,9 +58,11 @@ __host__ __device__ constexpr int sweeps(int epi) { return epi == kEpiSoftmax ? 
 // the tile's columns: one warp per scheduler cannot hide the latency of its own chain (TMEM
 // load, shuffles, mask bytes from HBM, stores), which was what held mbmm back (c3 216 ->
 // 199 us). The plain store epilogue is not what limits bmm and measured 6 % slower with
-// eight warps; the reducing epilogues keep one warp per row quarter because a row's state
-// has one owner.
-__host__ __device__ constexpr int epilogue_warps(int epi) { return epi == kEpiMask ? 8 : 4; }
+// eight warps; min and top-k keep one warp per row quarter because a row's state has one
+// owner. The softmax epilogue is arithmetic-bound (32 exponentials per row and chunk in
+// each sweep) and gains the most from the second warp (c3 operands: 555 -> 300 us); its two
+// warps per row exchange their running (maximum, sum) once per unit.
+__host__ __device__ constexpr int epilogue_warps(int epi) { return is_masked(epi) ? 8 : 4; }
 // warps: 0 ring producer, 1 MMA issuer, 2-5 splitters, then the epilogue warps, then one warp
 // that loads the resident A blocks
 __host__ __device__ constexpr int block_threads(int epi) { return 192 + 32 * epilogue_warps(epi) + 32; }
@@ -76,6 +78,7 @@ __device__ long long g_fbmm_trace[4][1024];
 #define FBMM_TRACE_DECL int trace_n_ = 0, trace2_n_ = 0
 #define FBMM_TRACE2(role) if (blockIdx.x == 0 && trace2_n_ < 1024) g_fbmm_trace[role][trace2_n_++] = clock64()
 #define FBMM_TRACE(role) if (blockIdx.x == 0 && trace_n_ < 1024) g_fbmm_trace[role][trace_n_++] = clock64()
+#define FBMM_TRACE_TAG(role, tag) if (blockIdx.x == 0 && threadIdx.x == 192 && trace2_n_ < 1024) g_fbmm_trace[role][trace2_n_++] = (clock64() << 3) | (tag)
 #define FBMM_PROF_DECL long long prof_t0_ = 0, prof_acc_[4] = {0, 0, 0, 0}, prof_x_[4] = {0, 0, 0, 0}, prof_x0_ = 0
 #ifdef FBMM_PROFILE_LIGHT
 #define FBMM_PROF_XBEGIN()
@@ -109,6 +112,7 @@ __device__ long long g_fbmm_trace[4][1024];
 #define FBMM_TRACE_DECL
 #define FBMM_TRACE(role)
 #define FBMM_TRACE2(role)
+#define FBMM_TRACE_TAG(role, tag)
 #define FBMM_PROF_DECL
 #define FBMM_PROF_XBEGIN()
 #define FBMM_PROF_XEND(i)
@@ -630,6 +634,9 @@ constexpr uint32_t kMaskStages = 2;
 constexpr uint32_t kMaskElemBytes = kTileM * 128u;       // 128 rows x 128 columns, one byte each
 constexpr uint32_t kMaskThreadBytes = 16u * 16u;         // one byte per 8 x 8 tile
 constexpr uint32_t kMaskStageBytes = kMaskElemBytes + 512u;
+// Softmax: the two epilogue warps that share a row (one per half of a tile's columns) exchange
+// their running (maximum, sum) between the sweeps: [unit parity][column half][128 rows] x 8 bytes.
+constexpr uint32_t kSoftmaxExchangeBytes = 2u * 2u * kTileM * 8u;
 
 struct SmemPlan {
   uint32_t a_bytes, stage_bytes, stages, epi_bytes, total;
@@ -638,12 +645,14 @@ struct SmemPlan {
 // keeps in shared memory (top-k staging, or the mask tiles).
 // `pair`: a CTA of a pair keeps one whole plane of each B tile plus half a plane (see PAIR below).
 __host__ __device__ inline SmemPlan make_smem_plan(bool a_resident, int kblocks, bool topk, uint32_t planes = 2u,
-                                                   bool mask_tiles = false, bool pair = false) {
+                                                   bool mask_tiles = false, bool pair = false,
+                                                   bool softmax = false) {
   SmemPlan p;
   const uint32_t b_bytes = pair ? kPlaneBytes + kPlaneBytes / 2u : planes * kPlaneBytes;
   p.a_bytes = a_resident ? static_cast<uint32_t>(kblocks) * planes * kPlaneBytes : 0u;
   p.stage_bytes = (a_resident ? 0u : planes * kPlaneBytes) + b_bytes;
   p.epi_bytes = topk ? kTopkStageBytes : (mask_tiles ? kMaskStages * kMaskStageBytes : 0u);
+  if (softmax) p.epi_bytes += kSoftmaxExchangeBytes;
   const uint32_t fixed = p.a_bytes + p.epi_bytes + kBarrierBytes + 1024u /* alignment slack */;
   uint32_t st = (kSmemLimit - fixed) / p.stage_bytes;
   p.stages = st > static_cast<uint32_t>(kMaxStages) ? static_cast<uint32_t>(kMaxStages) : st;
@@ -662,6 +671,7 @@ struct Barriers {
   uint64_t a_empty[kMaxResidentKBlocks];  // last MMA of the unit done reading it
   uint64_t mask_full[kMaskStages];        // mask tile landed
   uint64_t mask_empty[kMaskStages];       // epilogue done reading it
+  uint64_t xchg;                          // softmax: every epilogue warp has posted its (max, sum)
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -731,7 +741,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr uint32_t kPlanes = kHalf ? 1u : 2u;  // planes per operand tile in shared memory
   const bool mask_tma = is_masked(EPI) && epi.mask_tma != 0;
   constexpr int kSweeps = sweeps(EPI);
-  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, kPlanes, mask_tma, PAIR);
+  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, kPlanes, mask_tma, PAIR, EPI == kEpiSoftmax);
   const uint32_t stages = plan.stages;
   constexpr uint32_t kBPlane = kPlaneBytes;  // one plane of a B tile
   // offsets inside a ring stage. Single CTA: (A hi | A lo |) B hi | B lo. Pair: (A hi | A lo |)
@@ -779,6 +789,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       mbar_init(&bars->mask_full[s], 1);
       mbar_init(&bars->mask_empty[s], epilogue_warps(EPI));
     }
+    mbar_init(&bars->xchg, epilogue_warps(EPI));
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -823,14 +834,13 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     t1 = min(shape.n_tiles, t0 + shape.tiles_per_chunk);
   };
   // Block-mask test of the mask epilogue (kernels/mbmm.cu:251-255): a zero byte means
-  // the 128x128 tile is neither loaded nor multiplied.
-  auto block_live = [&](int b, int mb128, int t) -> bool {
-    if (mb128 * kTileM >= shape.M) return false;
-    return epi.block_mask[b * epi.bm_stride + static_cast<long long>(mb128) * epi.bm_cols + t] != 0;
-  };
+  // the 128x128 tile is neither loaded nor multiplied. (Every role asks once per tile. Keeping
+  // the bytes of a row block as a bit window in registers instead was measured and is slower:
+  // the four registers it pins cost the epilogue and the MMA thread more than the loads do.)
   auto tile_live = [&](int b, int mb, int t) -> bool {
     if (!is_masked(EPI)) return true;
-    return block_live(b, mb, t);
+    if (mb * kTileM >= shape.M) return false;
+    return epi.block_mask[b * epi.bm_stride + static_cast<long long>(mb) * epi.bm_cols + t] != 0;
   };
   // First and last live tile of a unit; false when the unit has none.
   auto live_range = [&](int b, int mb, int t0, int t1, int& first, int& last) -> bool {
@@ -922,7 +932,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (long long u = unit_first; u < units && ok; u += unit_step) {
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
-        if (!live_range(b, mb, t0, t1, first, last)) continue;
+        if (!live_range( b, mb, t0, t1, first, last)) continue;
         for (int sweep = 0; sweep < kSweeps; ++sweep)
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
@@ -1034,7 +1044,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (long long u = unit_first; u < units && ok; u += unit_step) {
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
-        if (!live_range(b, mb, t0, t1, first, last)) continue;
+        if (!live_range( b, mb, t0, t1, first, last)) continue;
         for (int sweep = 0; sweep < kSweeps; ++sweep)
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
@@ -1123,7 +1133,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (long long u = unit_first; u < units && ok; u += unit_step) {
       int b, mb, t0, t1, first, last;
       decode(u, b, mb, t0, t1);
-      if (!live_range(b, mb, t0, t1, first, last)) continue;
+      if (!live_range( b, mb, t0, t1, first, last)) continue;
       for (int sweep = 0; sweep < kSweeps; ++sweep)
       for (int t = first; t <= last && ok; ++t) {
         if (!tile_live(b, mb, t)) continue;
@@ -1168,6 +1178,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int row_in_tile = static_cast<int>(quarter * 32u + lane);
     const uint32_t lane_base = (quarter * 32u) << 16;
     uint32_t acc_stage = 0, acc_phase = 0, mstage = 0, mphase = 0;
+    uint32_t xparity = 0;  // softmax: parity of the exchange barrier = which half of its buffer is in use
     bool ok = true;
     FBMM_PROF_DECL;
     FBMM_TRACE_DECL;
@@ -1180,7 +1191,6 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                              ((reinterpret_cast<uintptr_t>(epi.element_mask) & 7) == 0);
     // top-k staging: 8-byte (value, column) entries, slot-major [slot][row]
     int2* stg = reinterpret_cast<int2*>(epi_smem);
-
     for (long long u = unit_first; u < units && ok; u += unit_step) {
       int b, mb, t0, t1;
       decode(u, b, mb, t0, t1);
@@ -1219,12 +1229,35 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       float sm_max = -INFINITY, sm_sum = 0.f, sm_inv = 0.f;
 
       for (int sweep = 0; sweep < kSweeps; ++sweep) {
-      if (EPI == kEpiSoftmax && sweep == 1) sm_inv = sm_sum > 0.f ? 1.f / sm_sum : 0.f;
+      if (EPI == kEpiSoftmax && sweep == 1) {
+        // The other half of this row's columns went through another warp: post this warp's
+        // (maximum, sum), wait until all eight warps have, and fold the partner's in.
+        float2* xb = reinterpret_cast<float2*>(epi_smem + plan.epi_bytes - kSoftmaxExchangeBytes) + xparity * 2 * kTileM;
+        const int half = static_cast<int>((warp - 6u) >> 2);
+        xb[half * kTileM + row_in_tile] = make_float2(sm_max, sm_sum);
+        warp_arrive(&bars->xchg);
+        ok = mbar_wait(&bars->xchg, xparity, abort_flag);
+        if (!ok) break;
+        const float2 o = xb[(half ^ 1) * kTileM + row_in_tile];
+        xparity ^= 1u;
+        const float mx = fmaxf(sm_max, o.x);
+        if (mx == -INFINITY) {  // the row keeps nothing: all zeros
+          sm_max = 0.f;
+          sm_inv = 0.f;
+        } else {
+          sm_sum = sm_sum * ex2_approx(sm_max - mx) + o.y * ex2_approx(o.x - mx);
+          sm_max = mx;
+          sm_inv = sm_sum > 0.f ? 1.f / sm_sum : 0.f;
+        }
+      }
       for (int t = t0; t < t1 && ok; ++t) {
         const int col_tile = t * TILE_N;
-        const bool live = tile_live(b, mb, t);  // loads and MMAs happen for this tile
+                FBMM_TRACE_TAG(3, 0);
+        const bool live = tile_live(b, mb, t);
+        if (live) { FBMM_TRACE_TAG(3, 1); }  // loads and MMAs happen for this tile
         if (!live) {
           // masked-out block: the product is defined as zero (mbmm.py:74 pre-zeroes C).
+          FBMM_PROF_BEGIN();
           if (EPI == kEpiMask || (EPI == kEpiSoftmax && sweep == 1)) {
             const int c_end = min(shape.N, col_tile + TILE_N);
             if (kHalf) {
@@ -1250,6 +1283,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int c = col_tile + chunk_first * 32; c < min(c_end, col_tile + chunk_end * 32); ++c) crow[c] = 0.f;
             }
           }
+          FBMM_PROF_END(3);
+          FBMM_TRACE_TAG(3, 2);
           continue;
         }
         // Mask bytes of a 32-column chunk for this lane after the lane-quad transpose (lane q
@@ -1276,13 +1311,17 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!mask_tma && mask_line_ok(col_tile + chunk_first * 32)) mask_fetch(col_tile + chunk_first * 32);
         const uint8_t* mask_tile = epi_smem + mstage * kMaskStageBytes;
         if (mask_tma) {
-            ok = mbar_wait(&bars->mask_full[mstage], mphase, abort_flag);
-            if (!ok) break;
+          FBMM_PROF_BEGIN();
+          ok = mbar_wait(&bars->mask_full[mstage], mphase, abort_flag);
+          FBMM_PROF_END(2);
+          if (!ok) break;
         }
+        FBMM_TRACE_TAG(3, 3);
         FBMM_PROF_BEGIN();
         ok = wait_gate(&bars->acc_full[acc_stage], acc_phase);
         FBMM_PROF_END(0);
         if (!ok) break;
+        FBMM_TRACE_TAG(3, 4);
         tcgen05_fence_after_sync();
         FBMM_PROF_BEGIN();
         const uint32_t acc_big = tmem_base + acc_stage * (2 * TILE_N) + lane_base;
@@ -1292,34 +1331,38 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           uint32_t rb[32], rs[32];
           unsigned char tmv[4];
           uint2 e8[4];
-          // softmax: bit j set when column j of this thread's row in the chunk survives all three
-          // masks (a zero thread-mask byte drops its 8 x 8 tile, a zero element byte the entry;
-          // columns past N never count). Read before the TMEM loads: after the last chunk's
-          // loads the mask stage goes back to the producer.
-          uint32_t keep = 0;
+          // softmax: the 32 element-mask bytes of this thread's row in the chunk, as 8 words, with
+          // the bytes of a dropped 8 x 8 tile (zero thread-mask byte), of columns past N and of
+          // rows past M cleared: a non-zero byte is a kept entry. Read before the TMEM loads: after
+          // the last chunk's loads the mask stage goes back to the producer.
+          uint32_t ew[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
+          uint32_t any_kept = 0;
           if (EPI == kEpiSoftmax) {
             const int kc0 = col_tile + c * 32;
+            uint32_t tmw = 0;
             if (mask_tma) {
+              // (rows past M and columns past N arrive zero-filled)
               const uint4 e0 = *reinterpret_cast<const uint4*>(mask_tile + row_in_tile * 128 + c * 32);
               const uint4 e1 = *reinterpret_cast<const uint4*>(mask_tile + row_in_tile * 128 + c * 32 + 16);
-              const uint32_t tmw =
-                  *reinterpret_cast<const uint32_t*>(mask_tile + kMaskElemBytes + (row_in_tile >> 3) * 16 + c * 4);
-              const uint32_t ew[8] = {e0.x, e0.y, e0.z, e0.w, e1.x, e1.y, e1.z, e1.w};
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const uint32_t eb = (ew[j >> 2] >> ((j & 3) * 8)) & 0xffu, tb = (tmw >> ((j >> 3) * 8)) & 0xffu;
-                keep |= ((eb != 0u && tb != 0u) ? 1u : 0u) << j;
-              }
+              tmw = *reinterpret_cast<const uint32_t*>(mask_tile + kMaskElemBytes + (row_in_tile >> 3) * 16 + c * 4);
+              ew[0] = e0.x; ew[1] = e0.y; ew[2] = e0.z; ew[3] = e0.w;
+              ew[4] = e1.x; ew[5] = e1.y; ew[6] = e1.z; ew[7] = e1.w;
             } else if (row_ok) {
               const unsigned char* tm =
                   epi.thread_mask + b * epi.tm_stride + static_cast<long long>(row >> 3) * epi.tm_cols + (kc0 >> 3);
               const unsigned char* em = epi.element_mask + b * epi.em_stride + static_cast<long long>(row) * shape.N + kc0;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (kc0 + j < shape.N && tm[j >> 3] != 0 && em[j] != 0) keep |= 1u << j;
+                if (kc0 + j < shape.N) ew[j >> 2] |= static_cast<uint32_t>(em[j]) << ((j & 3) * 8);
+#pragma unroll
+              for (int g = 0; g < 4; ++g)
+                if (kc0 + 8 * g < shape.N) tmw |= static_cast<uint32_t>(tm[g]) << (g * 8);
             }
-            if (kc0 + 32 > shape.N) keep &= (kc0 < shape.N) ? ((1u << (shape.N - kc0)) - 1u) : 0u;
-            if (!row_ok) keep = 0;
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              if (((tmw >> (g * 8)) & 0xffu) == 0u) ew[2 * g] = ew[2 * g + 1] = 0u;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) any_kept |= ew[g];
           }
           if (EPI == kEpiMask && mask_tma) {
             // lane q of a quad: columns [8q, 8q + 8) of the quad's four rows, which share one
@@ -1397,7 +1440,8 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
                   for (int j = 0; j < 8; ++j) {
                     const uint32_t w = j < 4 ? e8[i].x : e8[i].y;
-                    const float ef = static_cast<float>((w >> ((j & 3) * 8)) & 0xffu);
+                    // byte -> float without the conversion unit: 0x4B0000bb is 2^23 + bb
+                    const float ef = __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7540u | (j & 3))) - 8388608.0f;
                     v[8 * i + j] = tmv[i] != 0 ? v[8 * i + j] * ef : 0.f;
                   }
                 }
@@ -1458,26 +1502,37 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           } else if (EPI == kEpiSoftmax) {
-            // This thread's row, 32 columns; scores go to the exp2 domain: s = (a.b) * scale * log2(e).
+            // This thread's row, 32 columns; scores go to the exp2 domain, s = (a.b) * scale * log2(e),
+            // and dropped entries to -inf, whose exponential is an exact 0.
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= epi.softmax_scale_log2e;
+            for (int j = 0; j < 32; ++j)
+              v[j] = (ew[j >> 2] & (0xffu << ((j & 3) * 8))) != 0u ? v[j] * epi.softmax_scale_log2e : -INFINITY;
             if (sweep == 0) {
-              float cmax = -INFINITY;
+              if (any_kept != 0u) {
+                // (trees, not chains: a warp or two per scheduler cannot hide a 32-deep dependency)
+                float x[16];
 #pragma unroll
-              for (int j = 0; j < 32; ++j) cmax = ((keep >> j) & 1u) ? fmaxf(cmax, v[j]) : cmax;
-              if (cmax > sm_max) {  // (never true for a chunk that keeps nothing)
-                sm_sum *= exp2f(sm_max - cmax);  // exp2(-inf) = 0 on the first kept chunk
-                sm_max = cmax;
-              }
-              if (keep != 0u) {
-                float part = 0.f;
+                for (int j = 0; j < 16; ++j) x[j] = fmaxf(v[j], v[j + 16]);
 #pragma unroll
-                for (int j = 0; j < 32; ++j) part += ((keep >> j) & 1u) ? exp2f(v[j] - sm_max) : 0.f;
-                sm_sum += part;
+                for (int w = 8; w > 0; w >>= 1)
+#pragma unroll
+                  for (int j = 0; j < w; ++j) x[j] = fmaxf(x[j], x[j + w]);
+                if (x[0] > sm_max) {
+                  sm_sum *= ex2_approx(sm_max - x[0]);  // exp2(-inf) = 0 on the first kept chunk
+                  sm_max = x[0];
+                }
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = ex2_approx(v[j] - sm_max);
+#pragma unroll
+                for (int w = 16; w > 0; w >>= 1)
+#pragma unroll
+                  for (int j = 0; j < w; ++j) v[j] += v[j + w];
+                sm_sum += v[0];
               }
             } else {
+              // (sm_max is finite here: a row that keeps nothing got 0 at the start of the sweep)
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = ((keep >> j) & 1u) ? exp2f(v[j] - sm_max) * sm_inv : 0.f;
+              for (int j = 0; j < 32; ++j) v[j] = ex2_approx(v[j] - sm_max) * sm_inv;
               const bool line_path = c_lines_ok && col0 + 32 <= shape.N;
               if (line_path) {
                 // whole warp: after the transpose lane q of a lane quad holds columns [8q, 8q + 8)
@@ -1577,6 +1632,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           FBMM_PROF_XEND(1);
         }
         FBMM_PROF_END(1);
+        FBMM_TRACE_TAG(3, 5);
         if (threadIdx.x == 192) { FBMM_TRACE(1); }
         if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
         if (mask_tma && ++mstage == kMaskStages) { mstage = 0; mphase ^= 1u; }
@@ -1611,7 +1667,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (long long u = unit_first; u < units && ok; u += unit_step) {
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
-        if (!live_range(b, mb, t0, t1, first, last)) continue;
+        if (!live_range( b, mb, t0, t1, first, last)) continue;
         for (int kb = 0; kb < kblocks; ++kb) {
           // free as soon as the previous unit's last tile has finished with that k-block
           ok = wait_gate(&bars->a_empty[kb], a_phase ^ 1u);

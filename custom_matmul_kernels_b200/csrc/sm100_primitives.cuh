@@ -361,6 +361,13 @@ __device__ __forceinline__ void st_global_v8_streaming(float* p, float a0, float
                : "memory");
 }
 
+// 2^x by the hardware approximation (about 2 ulp; -inf gives +0, denormal results flush to 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // ----------------------------------------------------------------------------------
 // fp32 -> (hi, lo) split for 3xTF32. The tensor core reads only the sign, exponent and
 // top 10 mantissa bits of a tf32 operand, so hi = x with the low 13 mantissa bits
