@@ -708,9 +708,10 @@ __device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint
 //           (the small one) in both CTAs;
 //   narrow  A_lo x B_hi, N = 128: the even CTA supplies columns 0-63 of B_hi, the odd CTA
 //           columns 64-127 (a second copy of 8 KB per CTA, at a common offset).
-// Measured on resident operands: 762 cycles per 256 x 128 x 32 k-block (4 wide + 4 narrow,
-// commits included) against 1057 per 128 x 128 x 32 in a single CTA, i.e. 2.8 times the
-// rate per SM. Each CTA loads its own operands (24 KB of B per k-block instead of 32 KB, no
+// Measured on resident operands: 762 cycles per 256 x 128 x 32 k-block of a pair (4 wide + 4
+// narrow, commits included) against 1057 per 128 x 128 x 32 in a single CTA: both SMs of a
+// pair are busy for those 762 cycles, so per SM the gain is 1057 / 762 = 1.39, all of it from
+// the narrow MMA (64 cycles as half of a pair, 112 alone). Each CTA loads its own operands (24 KB of B per k-block instead of 32 KB, no
 // cluster fan-out of any copy); completion bytes of both CTAs are counted on the even CTA's
 // barrier, barriers that gate the MMAs live in the even CTA (the peer arrives on them through
 // the cluster window) and every commit goes to both CTAs. Needs pre-split planes and fp32

@@ -95,7 +95,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
 // proxy fences
 // ----------------------------------------------------------------------------------
 // Orders this thread's generic-proxy shared-memory writes before later async-proxy
-// accesses (tcgen05.mma operand reads, TMA stores).
+// accesses (tcgen05.mma operand reads).
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -120,26 +120,6 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const void* tmap, ui
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(bar)),
         "r"(c0), "r"(c1), "r"(c2), "l"(l2_policy)
       : "memory");
-}
-
-__device__ __forceinline__ void tma_store_3d(const void* tmap, const void* smem_src, int32_t c0,
-                                             int32_t c1, int32_t c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-      ::"l"(reinterpret_cast<uint64_t>(tmap)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() {
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-// Waits until at most N committed store groups still read their shared-memory source.
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void tma_store_wait_all() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ----------------------------------------------------------------------------------
