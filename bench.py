@@ -718,6 +718,56 @@ def run_ours(args):
 # ---------------------------------------------------------------------------------------
 # reference arm: the reference's semantics on the host cores
 # ---------------------------------------------------------------------------------------
+def reference_kernels_on_gpu():
+    """The reference's OWN kernels (kernels/bmm.cu, mbmm.cu, minbmm.cu compiled as its wrappers
+    compile them into oracle/_ref/ and launched with its grids) timed on this GPU on c1, c2 and
+    c3: the direct kernel-against-kernel figure beside the CPU arm. c4 and c5 cannot be launched
+    (gridDim.y overflows, minbmm.py:127-129), and kernels/topkbmm.cu is not run at all (it takes
+    a global spin mutex). Output buffers are created by the launch helper as the reference's
+    wrappers create them (zeros / +inf), inside the timed call."""
+    try:
+        from oracle import ref_kernels as K
+        from oracle import ref_semantics as R
+        from custom_matmul_kernels_b200 import make_masks
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+    if not torch.cuda.is_available():
+        return {"unavailable": "no GPU"}
+    if not K.available():
+        return {"unavailable": "oracle/_ref holds no cubins (python -m oracle.build_ref <reference root>)"}
+    dev = torch.device("cuda", 0)
+    out = {}
+    for name in ("c1", "c2", "c3"):
+        h = R.make_inputs(name)
+        A, B = h["A"].to(dev), h["B"].to(dev)
+        if name == "c1":
+            fn = lambda: K.min_bmm(A, B, 2)  # noqa: E731
+        elif name == "c2":
+            fn = lambda: K.bmm(A, B)  # noqa: E731
+        else:
+            masks = make_masks(h["mask"].to(dev))
+            fn = lambda: K.mbmm(A, B, *masks)  # noqa: E731
+        for _ in range(2):
+            fn()
+        ms = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            ms.append(e0.elapsed_time(e1))
+        l, m, k, n = SHAPES[name]
+        units = m if name == "c1" else l
+        out[name] = {"ms_per_call": statistics.mean(ms), "ms_best": min(ms), "value": units / (statistics.mean(ms) / 1e3),
+                     "unit": UNIT[name], "kernel": {"c1": "min_bmm_nn", "c2": "bmm_nn", "c3": "mbmm_nn"}[name]}
+        del A, B
+        torch.cuda.empty_cache()
+    out["note"] = ("the reference's SIMT fp32 kernels recompiled for sm_100a, one call = output fill + kernel; "
+                   "c4 and c5 are beyond the reference's grid limits")
+    return out
+
+
 def run_reference(args):
     rank, world = env_int("RANK", 0), env_int("WORLD_SIZE", 1)
     if rank != 0:
@@ -763,6 +813,8 @@ def run_reference(args):
                                             "(the reference's kernels need CuPy and a GPU)"},
         "e2e": {"value": value, "unit": UNIT[name], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if world == 1 and not args.no_per_config:
+        line["reference_kernels_on_this_gpu"] = reference_kernels_on_gpu()
     print(json.dumps(line), flush=True)
 
 
