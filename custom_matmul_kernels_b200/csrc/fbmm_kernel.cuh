@@ -1,5 +1,6 @@
 // Fused fp32 batched-matmul kernel for sm_100a: C[b] = A[b] @ B[b] with the epilogue
-// chosen at compile time (store / masked store / row-wise min+argmin / row-wise top-k).
+// chosen at compile time (store / masked store / masked row softmax / row-wise min+argmin /
+// row-wise top-k).
 //
 // Replaces the reference's SIMT tile kernels (kernels/bmm.cu:185, kernels/mbmm.cu:209,
 // kernels/minbmm.cu:348, kernels/topkbmm.cu:500 and their layout variants) with one
@@ -22,14 +23,16 @@
 //   warps 6-9   epilogue: tcgen05.ld both accumulators, add them, then store / mask /
 //               reduce. One thread owns one output row, so per-row min and top-k state
 //               never crosses threads (the mask epilogue, which keeps no state, runs
-//               warps 6-13, two per row quarter).
+//               warps 6-13, two per row quarter; so does the softmax epilogue, whose two
+//               warps per row exchange their running maximum and sum once per unit).
 //
 // Work is cut into units (batch, 128-row block, run of column tiles); CTA i processes
 // units i, i + gridDim.x, ... All four roles walk the same unit list.
 //
 // Variants (template parameters of the kernel): lo planes taken from global memory
-// instead of the splitters (PRESPLIT), and fp16 / bf16 operands multiplied as they are by
-// kind::f16 (DT).
+// instead of the splitters (PRESPLIT), clusters of two CTAs on 256-row blocks with
+// tcgen05.mma.cta_group::2 (PAIR; min and top-k on pre-split planes, K > 64), and fp16 / bf16
+// operands multiplied as they are by kind::f16 (DT).
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
