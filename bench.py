@@ -153,11 +153,15 @@ def host_inputs(name, rank, world):
         out["A"], out["B"] = A[:, r0:r1].contiguous(), B
         out["units"] = r1 - r0
         return out
-    # c5: columns of B sharded; B is generated in 64Ki-column pieces, every rank alike
-    c0, c1 = shard_range(n, world, rank, 128)
+    # c5: a grid of ranks: columns of B cut `cs` ways (the exchange stays inside each group of ranks that
+    # share rows), rows of A cut across the `rg` groups. B is generated in 64Ki-column pieces, every rank alike.
+    from custom_matmul_kernels_b200.sharding import topk_grid
+    rg, cs = topk_grid(world)
+    r0, r1 = shard_range(m, rg, rank // cs, 256)
+    c0, c1 = shard_range(n, cs, rank % cs, 128)
     A = torch.randn(l, m, k, generator=g)
     B = torch.empty(l, k, c1 - c0)
-    sample_rows = check_rows("c5", m)
+    sample_rows = check_rows("c5", r1 - r0) + r0
     prod = torch.zeros(len(sample_rows), n, dtype=torch.float64) if rank == 0 else None
     As = A[0, sample_rows].double() if rank == 0 else None
     piece = 65536
@@ -168,9 +172,10 @@ def host_inputs(name, rank, world):
             B[:, :, lo - c0:hi - c0] = blk[:, :, lo - p0:hi - p0]
         if rank == 0:  # the oracle's fp64 product of the sampled rows against ALL columns, piece by piece
             prod[:, p0:p0 + blk.shape[2]] = As @ blk[0].double()
-    out["A"], out["B"], out["col0"] = A, B, c0
-    out["cols_per_rank"] = shard_stride(n, world, 128)
-    out["units"] = m
+    out["A"], out["B"], out["col0"] = A[:, r0:r1].contiguous(), B, c0
+    out["cols_per_rank"] = shard_stride(n, cs, 128)
+    out["units"] = r1 - r0
+    out["grid"] = (rg, cs)
     out["check_product"] = prod
     return out
 
@@ -216,6 +221,7 @@ class Workload:
                 self.kernels_per_step += 1  # lo-plane pass over B (A is split in shared memory)
         else:
             self.op = TopkBMMCUDA()
+            self.group = sharding.make_column_groups(world, h["grid"][1], rank) if world > 1 else None
             self.kernels_per_step = 1 + (1 if world > 1 else 0)  # + candidate merge
             if n_ > 0 and self.op.lib.fbmm_presplit_workspace_bytes(l_, m_, n_, k_, 2, ord("n"), k_, m_ * k_, ord("n"), n_,
                                                                     k_ * n_):
@@ -234,7 +240,8 @@ class Workload:
         if self.world == 1:
             return self.op(A, B, k=TOPK, dim=2)
         return self.sharding.topk_bmm_column_sharded(
-            A, B, self.h["cols_per_rank"], TOPK, lambda a, b, k: self.op.packed(a, b, k=k, dim=2), timings=timings)
+            A, B, self.h["cols_per_rank"], TOPK, lambda a, b, k: self.op.packed(a, b, k=k, dim=2), group=self.group,
+            timings=timings)
 
     def step(self):
         timings = {} if (self.name == "c5" and self.world > 1) else None
@@ -487,8 +494,13 @@ def config_dict(name, world):
     """The same for both arms: what is computed, on what, cut how."""
     l, m, k, n = SHAPES[name]
     part = {"c1": "A rows", "c4": "A rows", "c2": "batches", "c3": "batches", "c5": "B columns + all-gather"}[name]
+    how = f"{part} over {world} GPU(s)"
+    if name == "c5" and world > 1:
+        from custom_matmul_kernels_b200.sharding import topk_grid
+        rg, cs = topk_grid(world)
+        how = f"B columns over {cs} GPUs (packed all-gather + merge)" + (f" x A rows over {rg} such groups" if rg > 1 else "")
     return {"workload": f"{name}: {OPS[name]} A[{l},{m},{k}] B[{l},{k},{n}]" + (f" k={TOPK}" if name == "c5" else ""),
-            "sharding": f"{part} over {world} GPU(s)", "precision": "fp32 in, fp32 out",
+            "sharding": how, "precision": "fp32 in, fp32 out",
             "l2": "flushed between steps" if name in ("c1", "c2", "c3") else "inputs exceed L2"}
 
 

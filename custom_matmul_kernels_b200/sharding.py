@@ -76,6 +76,40 @@ def column_shard(B: torch.Tensor, group=None) -> Tuple[torch.Tensor, int]:
 # high half = int32 shard-local column (-1 = empty slot). In memory (little endian) that is
 # { float value; int index; }, what fbmm_topk_bmm_packed_f32 writes.
 # ---------------------------------------------------------------------------------------
+# Column shards cost the top-k kernel efficiency as they get narrower (every row block restarts
+# its running lists, and the merges of the first tiles of a sweep hold up the MMAs: measured on one
+# B200, 1 048 576 rows, K = 256, k = 64: 231 TFLOP/s at 1 048 576 columns, 229 at 524 288, 217 at
+# 262 144, 206 at 131 072), and the exchange grows with the number of shards. So beyond
+# MAX_COLUMN_SHARDS ranks the ranks form a grid: columns of B are cut MAX_COLUMN_SHARDS ways (the
+# packed all-gather + merge stay in the data path, inside each group of ranks that share rows), and
+# the rows of A are cut across the groups, which need no communication at all.
+MAX_COLUMN_SHARDS = 2
+
+
+def topk_grid(world: int, max_column_shards: int = MAX_COLUMN_SHARDS) -> Tuple[int, int]:
+    """(row_groups, column_shards) of the rank grid for column-sharded top-k; rank r sits in row
+    group r // column_shards and holds column shard r % column_shards."""
+    c = max(1, min(world, max_column_shards))
+    while world % c:
+        c -= 1
+    return world // c, c
+
+
+def make_column_groups(world: int, column_shards: int, rank: int):
+    """One process group per row group (the ranks that hold the column shards of the same rows);
+    every rank has to call this, since creating a group is collective. Returns this rank's group
+    (None when a single group spans the world)."""
+    if column_shards == world:
+        return None
+    mine = None
+    for g in range(world // column_shards):
+        ranks = list(range(g * column_shards, (g + 1) * column_shards))
+        grp = dist.new_group(ranks=ranks)
+        if rank in ranks:
+            mine = grp
+    return mine
+
+
 def pack_candidates(values: torch.Tensor, local_indices: torch.Tensor) -> torch.Tensor:
     bits = values.contiguous().view(torch.int32).to(torch.int64) & 0xFFFFFFFF
     return (local_indices.to(torch.int64) << 32) | bits

@@ -136,3 +136,67 @@ def test_two_rank_gloo_partitions_match_single_device():
         p.join(120)
         assert p.exitcode == 0
     assert out.get() == "ok"
+
+
+def test_topk_grid_shapes():
+    assert S.topk_grid(1) == (1, 1)
+    assert S.topk_grid(2) == (1, 2)
+    assert S.topk_grid(4) == (2, 2)
+    assert S.topk_grid(8) == (4, 2)
+    assert S.topk_grid(3) == (3, 1)          # no way to cut 3 ranks into column pairs
+    assert S.topk_grid(8, max_column_shards=8) == (1, 8)
+
+
+def _grid_worker(rank, world, port, out):
+    """Four ranks as a 2 x 2 grid: columns of B cut two ways inside each row group (packed
+    all-gather + merge within the group), rows of A cut across the two groups."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = torch.Generator().manual_seed(9)
+        A = torch.randn(1, 512, 24, generator=g)
+        B = torch.randn(1, 24, 1000, generator=g)
+        k = 11
+        rg, cs = S.topk_grid(world)
+        assert (rg, cs) == (2, 2)
+        group = S.make_column_groups(world, cs, rank)
+        r0, r1 = S.shard_range(A.shape[1], rg, rank // cs, 256)
+        c0, c1 = S.shard_range(B.shape[2], cs, rank % cs, 128)
+        stride = S.shard_stride(B.shape[2], cs, 128)
+
+        def local_packed(a, b, kk):
+            v, i = R.topk_bmm(a, b, k=kk, dim=2)
+            return S.pack_candidates(v, i)
+
+        v, i = S.topk_bmm_column_sharded(A[:, r0:r1].contiguous(), B[:, :, c0:c1].contiguous(), stride, k, local_packed,
+                                         merge=S.merge_packed_torch, group=group)
+        wv, wi = R.topk_bmm(A, B, k=k, dim=2)
+        assert torch.equal(v, wv[:, r0:r1])
+        R.check_topk(v, i, A[:, r0:r1], B, k, 2)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (rank, r0, v))
+        if rank == 0:
+            # one rank of every row group: together they hold every row once
+            rows = torch.cat([x[2] for x in sorted(gathered) if x[0] % cs == 0], dim=1)
+            assert torch.equal(rows, wv)
+            out.put("ok")
+    except Exception as e:
+        if rank == 0:
+            out.put(f"fail: {e!r}")
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_four_rank_gloo_grid_matches_single_device():
+    ctx = mp.get_context("spawn")
+    out = ctx.SimpleQueue()
+    port = _free_port()
+    procs = [ctx.Process(target=_grid_worker, args=(r, 4, port, out)) for r in range(4)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    assert out.get() == "ok"
