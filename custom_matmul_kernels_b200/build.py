@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(HERE, "libfbmm.so")
 SOURCES = [os.path.join(CSRC, "fbmm_api.cu")]
 HEADERS = [
     os.path.join(CSRC, "fbmm_kernel.cuh"),
+    os.path.join(CSRC, "fbmm_l1_kernel.cuh"),
     os.path.join(CSRC, "sm100_primitives.cuh"),
     os.path.join(HERE, os.pardir, "include", "fbmm.h"),
 ]

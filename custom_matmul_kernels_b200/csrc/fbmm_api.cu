@@ -12,6 +12,7 @@
 
 #include "../../include/fbmm.h"
 #include "fbmm_kernel.cuh"
+#include "fbmm_l1_kernel.cuh"
 
 namespace {
 
@@ -404,9 +405,38 @@ int launch_norms(cudaStream_t stream, const RowProblem& p, void* scratch, EpiArg
   return FBMM_OK;
 }
 
-int check_distance(int distance) {
-  if (distance != FBMM_DIST_INNER && distance != FBMM_DIST_L2)
-    return fail(FBMM_ERR_INVALID, "distance must be FBMM_DIST_INNER (0) or FBMM_DIST_L2 (1), got %d", distance);
+// `l1_ok`: the entry point has the SIMT l1 path behind it (fp32 min and top-k); the 16-bit entries do not.
+int check_distance(int distance, bool l1_ok = true) {
+  if (distance == FBMM_DIST_L1 && !l1_ok)
+    return fail(FBMM_ERR_UNSUPPORTED, "FBMM_DIST_L1 is available for fp32 operands only");
+  if (distance != FBMM_DIST_INNER && distance != FBMM_DIST_L2 && distance != FBMM_DIST_L1)
+    return fail(FBMM_ERR_INVALID, "distance must be FBMM_DIST_INNER (0), FBMM_DIST_L2 (1) or FBMM_DIST_L1 (2), got %d", distance);
+  return FBMM_OK;
+}
+
+// The l1 mode: the SIMT kernel of fbmm_l1_kernel.cuh on the same units, outputs and scratch as
+// the tensor-core kernel. Top-k CTAs own a slot of running lists each, so there are at most `sms`
+// of them; min CTAs are small enough for two per SM.
+template <int EPI, int E>
+int launch_l1(cudaStream_t stream, const DeviceState& st, const RowProblem& p, const GemmShape& shape, const EpiArgs& epi) {
+  L1Operand oa{p.a.ptr, p.a.ld, p.L > 1 ? p.a.stride : 0, p.a.mn_major ? 1 : 0, p.M};
+  L1Operand ob{p.b.ptr, p.b.ld, p.L > 1 ? p.b.stride : 0, p.b.mn_major ? 1 : 0, p.N};
+  const uint32_t smem = l1_smem_bytes(EPI);
+  static std::mutex mu;
+  static bool attr_set[kMaxDevices] = {};
+  {
+    int dev = 0;
+    FBMM_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(mu);
+    if (!attr_set[dev]) {
+      FBMM_CUDA(cudaFuncSetAttribute(fbmm_l1_kernel<EPI, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+      attr_set[dev] = true;
+    }
+  }
+  const long long workers = EPI == kEpiTopk ? st.sms : 2ll * st.sms;
+  const unsigned grid = static_cast<unsigned>(shape.num_units < workers ? shape.num_units : workers);
+  fbmm_l1_kernel<EPI, E><<<grid, kL1Threads, smem, stream>>>(oa, ob, shape, epi);
+  FBMM_CUDA(cudaGetLastError());
   return FBMM_OK;
 }
 
@@ -686,11 +716,13 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   // room behind the op's own scratch for the lo planes? then the operands are split once up
   // front and the kernel runs as CTA pairs on 256-row blocks
   const size_t lo_off = align_up(need, 256);
-  const bool presplit = presplit_worthwhile(p) && (b_planes_fit_l2(p) || p.L == 1) && workspace_bytes >= lo_off + presplit_bytes(p);
+  const bool l1 = distance == FBMM_DIST_L1;  // SIMT kernel: no planes, no pairs
+  const bool presplit = !l1 && presplit_worthwhile(p) && (b_planes_fit_l2(p) || p.L == 1) &&
+                        workspace_bytes >= lo_off + presplit_bytes(p);
   const bool pairs = pairs_apply(p, presplit);
   GemmShape s = base_shape(p, pairs);
-  choose_chunks(l, s.m_blocks, s.n_tiles, unit_workers(st->sms, pairs), kMinOverheadTiles, kMaxChunks, &s.n_chunks,
-                &s.tiles_per_chunk);
+  choose_chunks(l, s.m_blocks, s.n_tiles, l1 ? 2 * st->sms : unit_workers(st->sms, pairs), kMinOverheadTiles, kMaxChunks,
+                &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   const long long rows = static_cast<long long>(l) * p.M;
   unsigned long long* keys = static_cast<unsigned long long*>(workspace);
@@ -719,7 +751,9 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
       s.chunk_major = 1;
     }
   }
-  if ((rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e, lo_scratch, pairs)) != FBMM_OK) return rc;
+  if (l1) rc = launch_l1<kEpiMin, 1>(stream, *st, p, s, e);
+  else rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e, lo_scratch, pairs);
+  if (rc != FBMM_OK) return rc;
   const int threads = 256;
   const long long blocks = (rows + threads - 1) / threads;
   fbmm_min_finalize_kernel<<<static_cast<unsigned>(blocks), threads, 0, stream>>>(keys, values, indices, rows);
@@ -846,7 +880,8 @@ int topk_bmm_impl(cudaStream_t stream, const float* A, int a_layout, long long l
   // CTA pairs on pre-split planes when the workspace has room for the planes behind the op's
   // own scratch; a column operand wider than L2 also needs the one-chunk sweep, which can be paced
   TopkLayout lay = topk_layout(l, p.M, p.N, k, topk, distance, st->sms, true);
-  const bool presplit = p.M > kTileM && presplit_worthwhile(p) && (b_planes_fit_l2(p) || lay.n_chunks == 1) &&
+  const bool l1 = distance == FBMM_DIST_L1;  // SIMT kernel: no planes, no pairs, no pacing
+  const bool presplit = !l1 && p.M > kTileM && presplit_worthwhile(p) && (b_planes_fit_l2(p) || lay.n_chunks == 1) &&
                         workspace_bytes >= lay.own + presplit_bytes(p);
   const bool pairs = pairs_apply(p, presplit);
   if (!pairs) lay = topk_layout(l, p.M, p.N, k, topk, distance, st->sms, false);
@@ -883,7 +918,11 @@ int topk_bmm_impl(cudaStream_t stream, const float* A, int a_layout, long long l
       FBMM_CUDA(cudaMemsetAsync(s.pace_counts, 0, lay.pace.count_bytes, stream));
     }
   }
-  if (topk <= 32) rc = launch_gemm<kEpiTopk, 1>(stream, *st, p, s, e, lo_scratch, pairs);  // E: blocks of 32 list entries per row
+  if (l1) {
+    if (topk <= 32) rc = launch_l1<kEpiTopk, 1>(stream, *st, p, s, e);
+    else if (topk <= 64) rc = launch_l1<kEpiTopk, 2>(stream, *st, p, s, e);
+    else rc = launch_l1<kEpiTopk, 4>(stream, *st, p, s, e);
+  } else if (topk <= 32) rc = launch_gemm<kEpiTopk, 1>(stream, *st, p, s, e, lo_scratch, pairs);  // E: blocks of 32 list entries per row
   else if (topk <= 64) rc = launch_gemm<kEpiTopk, 2>(stream, *st, p, s, e, lo_scratch, pairs);
   else rc = launch_gemm<kEpiTopk, 4>(stream, *st, p, s, e, lo_scratch, pairs);
   if (rc != FBMM_OK) return rc;
@@ -1287,7 +1326,7 @@ extern "C" int fbmm_min_bmm_x16(void* stream_, const void* A, long long lda, lon
   int rc;
   if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
   if ((rc = check_dtype_x16(dtype)) != FBMM_OK) return rc;
-  if ((rc = check_distance(distance)) != FBMM_OK) return rc;
+  if ((rc = check_distance(distance, false)) != FBMM_OK) return rc;
   if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
   RowProblem p;
   if ((rc = make_row_problem_x16(&p, A, lda, stride_a, B, ldb, stride_b, l, m, n, k, dim)) != FBMM_OK) return rc;
@@ -1325,7 +1364,7 @@ extern "C" int fbmm_topk_bmm_x16(void* stream_, const void* A, long long lda, lo
   int rc;
   if ((rc = check_dims(l, m, n, k)) != FBMM_OK) return rc;
   if ((rc = check_dtype_x16(dtype)) != FBMM_OK) return rc;
-  if ((rc = check_distance(distance)) != FBMM_OK) return rc;
+  if ((rc = check_distance(distance, false)) != FBMM_OK) return rc;
   if (topk <= 0 || topk > 128) return fail(FBMM_ERR_INVALID, "topk must be in 1..128, got %d", topk);
   if (values == nullptr || indices == nullptr) return fail(FBMM_ERR_INVALID, "values or indices is null");
   RowProblem p;

@@ -28,18 +28,20 @@ FBMM_ERR_PEER = -7
 FBMM_ERR_COMM = -8
 FBMM_DIST_INNER = 0
 FBMM_DIST_L2 = 1
+FBMM_DIST_L1 = 2
 
 
 def distance_code(distance: str) -> int:
-    """The reference's `distance` strings (minbmm.py:12-19): inner and l2 are built; l1 has
-    no matrix-product form and stays unimplemented; anything else is an error (the
-    reference builds that ValueError but never raises it, minbmm.py:19)."""
+    """The reference's `distance` strings (minbmm.py:12-19). inner and l2 run on the tensor
+    cores; l1 has no matrix-product form and runs as a SIMT kernel (fp32 operands only);
+    anything else is an error (the reference builds that ValueError but never raises it,
+    minbmm.py:19)."""
     if distance == "inner":
         return FBMM_DIST_INNER
     if distance in ("l2", "euclidean"):
         return FBMM_DIST_L2
     if distance in ("l1", "manhattan"):
-        raise NotImplementedError("distance='l1' is not implemented (no tensor-core form); use 'inner' or 'l2'")
+        return FBMM_DIST_L1
     raise ValueError("Unrecognized distance type")
 
 _c_ll = ctypes.c_longlong

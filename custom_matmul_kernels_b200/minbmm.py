@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .custom_kernel import (CustomKernel, check, distance_code, dtype_code_x16, layout_letter, operand,
+from .custom_kernel import (FBMM_DIST_L1, CustomKernel, check, distance_code, dtype_code_x16, layout_letter, operand,
                             operand_x16)
 
 _X16 = (torch.float16, torch.bfloat16)
@@ -18,7 +18,8 @@ class MinBMMCUDA(CustomKernel):
     values are fp32, indices int64. Ties resolve to the lowest index (the reference is
     racy there, kernels/minbmm.cu:76-79). distance="inner" reduces the products,
     distance="l2"/"euclidean" the squared distances sum_k (A[m,k] - B[k,n])^2
-    (minbmm.py:12-19); "l1" is not implemented."""
+    (minbmm.py:12-19), distance="l1"/"manhattan" the sums sum_k |A[m,k] - B[k,n]|
+    (minbmm.py:16-17; fp32 tensors only: a SIMT kernel, the tensor cores cannot form |a - b|)."""
 
     def __init__(self, patch_m=4, patch_n=4, distance="inner"):
         super().__init__()
@@ -41,6 +42,8 @@ class MinBMMCUDA(CustomKernel):
         values = torch.empty((l, rows), device=A3.device, dtype=torch.float32)
         indices = torch.empty((l, rows), device=A3.device, dtype=torch.int64)
         if A3.dtype in _X16:
+            if self._distance_code == FBMM_DIST_L1:
+                raise NotImplementedError("distance='l1' takes fp32 tensors only")
             # fp16 / bf16 go to the tensor cores as they are; values come back in fp32
             a_keep, lda, sa = operand_x16(A3)
             b_keep, ldb, sb = operand_x16(B3.transpose(1, 2))

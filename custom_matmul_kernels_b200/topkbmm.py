@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from .custom_kernel import (CustomKernel, check, distance_code, dtype_code_x16, layout_letter, operand,
+from .custom_kernel import (FBMM_DIST_L1, CustomKernel, check, distance_code, dtype_code_x16, layout_letter, operand,
                             operand_x16)
 
 _X16 = (torch.float16, torch.bfloat16)
@@ -18,8 +18,9 @@ class TopkBMMCUDA(CustomKernel):
     (topkbmm.py:104). Outputs are contiguous (the reference returns [:,:,:k] views of
     128-wide buffers, topkbmm.py:150-151). Any m and n are handled; where fewer than k
     entries exist the tail is -inf / -1. distance="l2" ranks the squared distances
-    sum_k (A[m,k] - B[k,n])^2 (largest first, as the reference does, topkbmm.py:17-18); "l1"
-    is not implemented."""
+    sum_k (A[m,k] - B[k,n])^2 (largest first, as the reference does, topkbmm.py:17-18),
+    distance="l1" the sums sum_k |A[m,k] - B[k,n]| (topkbmm.py:19-20; fp32 tensors only: a SIMT
+    kernel, the tensor cores cannot form |a - b|)."""
 
     def __init__(self, patch_m=4, patch_n=4, distance="inner"):
         super().__init__()
@@ -44,6 +45,8 @@ class TopkBMMCUDA(CustomKernel):
         values = torch.empty((l, rows, k), device=A3.device, dtype=torch.float32)
         indices = torch.empty((l, rows, k), device=A3.device, dtype=torch.int64)
         if A3.dtype in _X16:
+            if self._distance_code == FBMM_DIST_L1:
+                raise NotImplementedError("distance='l1' takes fp32 tensors only")
             # fp16 / bf16 go to the tensor cores as they are; values come back in fp32
             a_keep, lda, sa = operand_x16(A3)
             b_keep, ldb, sb = operand_x16(B3.transpose(1, 2))

@@ -48,9 +48,11 @@ extern "C" {
 /* `distance` of min_bmm / topk_bmm, the reference's accumulate functions
  * (minbmm.py:12-19, kernels/bmm_helpers.cu:20-35): inner product (madd) or squared
  * Euclidean distance sum_k (a - b)^2 (squared_l2), computed on the tensor cores as
- * |a|^2 + |b|^2 - 2 a.b. The l1 variants have no matrix-product form and are not built. */
+ * |a|^2 + |b|^2 - 2 a.b. The l1 distance sum_k |a - b| (l1) has no matrix-product form: it
+ * runs as a plain fp32 SIMT tile kernel with the same epilogues, outputs and workspace. */
 #define FBMM_DIST_INNER 0
 #define FBMM_DIST_L2 1
+#define FBMM_DIST_L1 2   /* sum_k |a - b| (kernels/bmm_helpers.cu:46-52): fp32 min and top-k only, a SIMT kernel */
 
 /* Element types of the *_x16 entry points. */
 #define FBMM_F16 1

@@ -135,8 +135,7 @@ def test_wrappers_reject_bad_inputs_on_cpu():
             op(A.half(), B)  # dtypes differ
         with pytest.raises(ValueError):
             op(A[0], B)
-    with pytest.raises(NotImplementedError):
-        MinBMMCUDA(distance="l1")
+    assert MinBMMCUDA(distance="l1")._distance_code == 2 and TopkBMMCUDA(distance="manhattan")._distance_code == 2
     assert MinBMMCUDA(distance="euclidean")._distance_code == 1 and TopkBMMCUDA(distance="l2")._distance_code == 1
     with pytest.raises(ValueError):
         TopkBMMCUDA(distance="cosine")

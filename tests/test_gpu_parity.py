@@ -649,6 +649,55 @@ def test_l2_distance_exact_and_nonnegative(dev, lib):
     device_ok(lib)
 
 
+# ----------------------------------------------------------------------------- l1 distance
+@pytest.mark.parametrize("shape", [(1, 200, 40, 300), (2, 130, 64, 257), (1, 1100, 19, 1300), (1, 64, 200, 5200),
+                                   (3, 1, 1, 1)])
+def test_min_and_topk_l1_distance(dev, lib, shape):
+    """distance="l1": sum_k |a - b| (l1 of the reference, kernels/bmm_helpers.cu:46-52), the SIMT
+    kernel: both dims, all four layouts for one shape, k below and above 32 and 64, shapes with
+    ragged rows / columns / K, several column chunks per row block (64 x 5200), 1 x 1 x 1;
+    against the direct fp64 formula."""
+    from custom_matmul_kernels_b200 import MinBMMCUDA, TopkBMMCUDA
+    l, m, k, n = shape
+    g = torch.Generator().manual_seed(sum(shape) + 3)
+    A, B = torch.randn(l, m, k, generator=g), torch.randn(l, k, n, generator=g)
+    mn, tk = MinBMMCUDA(distance="l1"), TopkBMMCUDA(distance="manhattan")
+    combos = layouts(A.to(dev), B.to(dev)) if shape[1] == 200 else {"nn": (A.to(dev), B.to(dev))}
+    for mode, (a, b) in combos.items():
+        for dim in (1, 2):
+            v, i = mn(a, b, dim=dim)
+            R.check_min(v, i, A, B, dim, distance="l1")
+            for kk in (9, 40, 100):
+                tv, ti = tk(a, b, k=kk, dim=dim)
+                R.check_topk(tv, ti, A, B, kk, dim, distance="l1")
+    device_ok(lib)
+
+
+def test_l1_distance_exact_packed_and_16_bit(dev, lib):
+    """Integer operands: every l1 distance is an exact integer, so values and min indices match the
+    oracle bit for bit and a column equal to a row gives exactly 0; the packed candidates equal the
+    unpacked result; 16-bit tensors are refused."""
+    from custom_matmul_kernels_b200 import MinBMMCUDA, TopkBMMCUDA
+    from custom_matmul_kernels_b200 import sharding as S
+    A, B = R.exact_inputs(2, 140, 24, 300, seed=43, lo=-4, hi=4)
+    B[0, :, 17] = A[0, 5]
+    v, i = MinBMMCUDA(distance="l1")(A.to(dev), B.to(dev), dim=2)
+    wv, wi = R.min_bmm(A, B, dim=2, distance="l1")
+    assert torch.equal(v.cpu(), wv) and torch.equal(i.cpu(), wi)
+    assert float(v[0, 5]) == 0.0 and bool((v >= 0).all())
+    op = TopkBMMCUDA(distance="l1")
+    tv, ti = op(A.to(dev), B.to(dev), k=12, dim=2)
+    wtv, _ = R.topk_bmm(A, B, k=12, dim=2, distance="l1")
+    assert torch.equal(tv.cpu(), wtv)
+    pv, pi = S.unpack_candidates(op.packed(A.to(dev), B.to(dev), k=12, dim=2))
+    assert torch.equal(pv, tv) and torch.equal(pi, ti)
+    with pytest.raises(NotImplementedError):
+        MinBMMCUDA(distance="l1")(A.to(dev).half(), B.to(dev).half(), dim=2)
+    with pytest.raises(NotImplementedError):
+        op(A.to(dev).bfloat16(), B.to(dev).bfloat16(), k=4, dim=2)
+    device_ok(lib)
+
+
 def test_every_op_on_shapes_that_straddle_row_blocks(dev, lib):
     """A spread of ops, layouts and both dims on shapes with several row blocks and ragged
     edges (300, 1100 and 129 rows), each against the oracle."""

@@ -79,6 +79,12 @@ def test_reference_min_kernels_pin_the_oracle_and_the_library(ref, dev, lib):
     wv, _ = c_oracle.min_bmm(A, B, 2, "l1")
     rv, _ = ref.min_bmm(Ad, Bd, 2, "nn", "l1")
     assert torch.equal(rv.cpu(), wv)
+    # ... and the library's l1 kernel against the reference's (both dims)
+    for dim in (1, 2):
+        rv, _ = ref.min_bmm(Ad, Bd, dim, "nn", "l1")
+        v, i = MinBMMCUDA(distance="l1")(Ad, Bd, dim=dim)
+        assert tol_ratio(v, rv) <= 2.0, dim
+        R.check_min(v, i, A, B, dim, distance="l1")
     assert lib.fbmm_check(None) == 0
 
 
