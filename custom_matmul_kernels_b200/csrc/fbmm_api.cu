@@ -721,8 +721,10 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
                         workspace_bytes >= lo_off + presplit_bytes(p);
   const bool pairs = pairs_apply(p, presplit);
   GemmShape s = base_shape(p, pairs);
-  choose_chunks(l, s.m_blocks, s.n_tiles, l1 ? 2 * st->sms : unit_workers(st->sms, pairs), kMinOverheadTiles, kMaxChunks,
-                &s.n_chunks, &s.tiles_per_chunk);
+  // (an l1 tile costs so many fp32 instructions that an extra unit costs nothing beside it: the
+  // column sweep is cut as finely as balances the 2 x sms CTAs best)
+  choose_chunks(l, s.m_blocks, s.n_tiles, l1 ? 2 * st->sms : unit_workers(st->sms, pairs), l1 ? 0 : kMinOverheadTiles,
+                kMaxChunks, &s.n_chunks, &s.tiles_per_chunk);
   s.num_units = static_cast<long long>(l) * s.m_blocks * s.n_chunks;
   const long long rows = static_cast<long long>(l) * p.M;
   unsigned long long* keys = static_cast<unsigned long long*>(workspace);
