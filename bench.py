@@ -686,6 +686,48 @@ def measure_softmax_consumer(args, dev):
                       "tolerance": "abs 2e-6 + rel 1e-4 on the probabilities, 3 batches, fp64 oracle"}}
 
 
+def measure_l1_mode(args, dev):
+    """distance="l1" (the SIMT kernel) on configuration 1's operands: min and top-64 over
+    sum_k |a - b|, device-timed with an L2 flush between steps, 64 sampled rows checked against the
+    fp64 formula. One GPU only (an extra, not a headline). The roofline is the fp32 issue rate:
+    two instructions per term on 128 lanes per SM at the sampled SM clock's maximum."""
+    from custom_matmul_kernels_b200 import MinBMMCUDA, TopkBMMCUDA
+    from oracle import ref_semantics as R
+    h = host_inputs("c1", 0, 1)
+    A, B = h["A"].to(dev), h["B"].to(dev)
+    l, m, k, n = SHAPES["c1"]
+    mn, tk = MinBMMCUDA(distance="l1"), TopkBMMCUDA(distance="l1")
+    flush = torch.zeros(L2_BYTES * 2 // 4, device=dev)
+    steps = args.steps if args.consumer_only else max(min(args.steps, 20), 10)
+    out = {"op": "min_bmm / topk_bmm with distance='l1' on the c1 operands", "steps": steps}
+    rows = check_rows("c1", m)[:64]
+    want = (h["A"][0, rows].double()[:, None, :] - h["B"][0].double().t()[None, :, :]).abs().sum(-1)  # [64, n]
+    for tag, fn in (("min", lambda: mn(A, B, dim=2)), ("top64", lambda: tk(A, B, k=TOPK, dim=2))):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        ms = timed_steps(fn, steps, flush)
+        v, i = fn()
+        gv, gi = v[0].cpu()[rows].double(), i[0].cpu()[rows]
+        if tag == "min":
+            wv = want.min(dim=1).values
+            at = want.gather(1, gi[:, None])[:, 0]
+            bad = int(((gv - wv).abs() > R.ATOL + R.RTOL * wv.abs()).sum()) + int(((at - wv).abs() > R.ATOL + R.RTOL * wv.abs()).sum())
+        else:
+            wv = want.topk(TOPK, dim=1).values
+            at = want.gather(1, gi)
+            bad = int(((gv - wv).abs() > R.ATOL + R.RTOL * wv.abs()).sum()) + int(((at - gv).abs() > R.ATOL + R.RTOL * gv.abs()).sum())
+        mean = statistics.mean(ms)
+        terms = float(l) * m * n * k
+        peak = 148 * 128 * 1.965e9 / 2.0  # terms/s if every fp32 issue slot did useful work at the maximum clock
+        out[tag] = {"ms_per_step": mean, "ms_per_step_best": min(ms), "rows_per_s": m / (mean / 1e3),
+                    "terms_per_s": terms / (mean / 1e3), "frac_of_fp32_issue_rate": terms / (mean / 1e3) / peak,
+                    "unexplained": bad, "ok": bad == 0}
+    out["checked"] = "64 rows against all 16384 columns, fp64 formula, rel 1e-5 / abs 1e-4"
+    del A, B, flush
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_ours(args):
     rank, local_rank, world = env_int("RANK", 0), env_int("LOCAL_RANK", 0), env_int("WORLD_SIZE", 1)
     torch.cuda.set_device(local_rank)
@@ -702,7 +744,7 @@ def run_ours(args):
                 per[other] = measure(other, args, rank, local_rank, world, dev, False)
     consumers = None
     if world == 1 and not args.no_per_config:
-        consumers = {"c3_softmax": measure_softmax_consumer(args, dev)}
+        consumers = {"c3_softmax": measure_softmax_consumer(args, dev), "c1_l1": measure_l1_mode(args, dev)}
     if rank == 0:
         line = {
             "metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world,
@@ -719,7 +761,7 @@ def run_ours(args):
             line["gpu_launches"] += sum(p["gpu_launches"] for p in per.values())
         if consumers:
             line["consumers"] = consumers
-            line["gpu_launches"] += consumers["c3_softmax"]["steps"]
+            line["gpu_launches"] += consumers["c3_softmax"]["steps"] + 2 * consumers["c1_l1"]["steps"]
         if args.rows is not None or args.batches is not None:
             line["reduced"] = True
         print(json.dumps(line), flush=True)
@@ -844,9 +886,9 @@ def main():
     ap.add_argument("--batches", type=int, default=None,
                     help="profiling only: cut c2/c3 to this many batches (the line is marked reduced)")
     ap.add_argument("--no-e2e", action="store_true", help="profiling only: skip the end-to-end legs")
-    ap.add_argument("--consumer-only", action="store_true",
-                    help="profiling only: run just the masked row softmax on the c3 operands (honours --batches) "
-                         "and print its record")
+    ap.add_argument("--consumer-only", nargs="?", const="softmax", default=None, choices=["softmax", "l1"],
+                    help="profiling only: run just the masked row softmax on the c3 operands (honours --batches), or "
+                         "just the l1 mode on the c1 operands, and print its record")
     args = ap.parse_args()
     if args.steps is None:
         args.steps = {"c1": 50, "c2": 30, "c3": 30, "c4": 10, "c5": 4}[args.workload]
@@ -860,7 +902,9 @@ def main():
         args.no_per_config = True
     if args.consumer_only:
         torch.cuda.set_device(0)
-        print(json.dumps({"consumers": {"c3_softmax": measure_softmax_consumer(args, torch.device("cuda", 0))}}))
+        dev0 = torch.device("cuda", 0)
+        rec = {"c1_l1": measure_l1_mode(args, dev0)} if args.consumer_only == "l1" else {"c3_softmax": measure_softmax_consumer(args, dev0)}
+        print(json.dumps({"consumers": rec}))
         return
     if args.impl == "reference":
         run_reference(args)
