@@ -67,6 +67,9 @@ def test_topk_and_min_validation(lib):
     assert rc == ck.FBMM_ERR_WORKSPACE
     rc = lib.fbmm_min_bmm_f32(None, 64, ord("n"), 4, 16, 64, ord("n"), 4, 16, 64, 64, 1, 4, 4, 4, 2, 7, None, 0)
     assert rc == ck.FBMM_ERR_INVALID and b"distance" in lib.fbmm_last_error()
+    # FBMM_DIST_L1 (2) is an fp32 mode: the 16-bit entries refuse it before touching anything
+    rc = lib.fbmm_min_bmm_x16(None, 64, 8, 32, 64, 8, 32, 1, 64, 64, 1, 4, 4, 8, 2, 2, None, 0)
+    assert rc == ck.FBMM_ERR_UNSUPPORTED and b"fp32" in lib.fbmm_last_error()
     rc = lib.fbmm_topk_merge_f32(None, 64, 64, 0, 4, 8, 64, 64)
     assert rc == ck.FBMM_ERR_INVALID
 
