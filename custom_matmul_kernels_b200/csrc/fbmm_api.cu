@@ -69,6 +69,11 @@ int set_smem_attr() {
     if ((rc = set_one_attr<EPI, E, false, kPs, kPs>()) != FBMM_OK) return rc;
     if ((rc = set_one_attr<EPI, E, true, kPs, kPs>()) != FBMM_OK) return rc;
   }
+  if (EPI == kEpiMin) {
+    constexpr bool kMin = EPI == kEpiMin;
+    FBMM_CUDA(cudaFuncSetAttribute(fbmm_gemm_kernel<EPI, E, true, kMin, 0, false, kMin>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemLimit)));
+  }
   return FBMM_OK;
 }
 
@@ -448,6 +453,14 @@ int launch_l1(cudaStream_t stream, const DeviceState& st, const RowProblem& p, c
 // with two k-blocks per tile the accumulator hand-off between the issuing CTA and BOTH epilogues
 // (one of them across the cluster) comes round too often. Pairs are used from K = 65 up.
 bool pairs_apply(const RowProblem& p, bool presplit) { return presplit && p.M > kTileM && p.K > 2 * kKBlock; }
+// Two resident row blocks of A per CTA (the kernel's DUAL notes): min on pre-split planes, at most
+// two k-blocks, at least 256 rows.
+bool dual_rows_apply(const RowProblem& p, bool presplit) {
+#ifdef FBMM_NO_DUAL
+  return false;
+#endif
+  return presplit && p.M >= 2 * kTileM && 2 * ((p.K + kKBlock - 1) / kKBlock) <= kMaxResidentKBlocks;
+}
 int rows_per_block(bool pairs) { return pairs ? 2 * kTileM : kTileM; }
 int unit_workers(int sms, bool pairs) { return pairs ? sms / 2 : sms; }
 
@@ -457,7 +470,7 @@ int unit_workers(int sms, bool pairs) { return pairs ? sms / 2 : sms; }
 // must then have been laid out in 256-row blocks).
 template <int EPI, int E>
 int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p, GemmShape shape, const EpiArgs& epi,
-                void* lo_scratch = nullptr, bool pairs = false) {
+                void* lo_scratch = nullptr, bool pairs = false, bool dual = false) {
   CUtensorMap ta, tb, ta_lo, tb_lo;
   int rc;
   EpiArgs epi_args = epi;
@@ -518,7 +531,10 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
     if ((rc = make_mask_maps(&tem, &ttm, epi, p.L, p.M, p.N)) != FBMM_OK) return rc;
     epi_args.mask_tma = 1;
   }
-  const SmemPlan plan = make_smem_plan(a_resident, kblocks, EPI == kEpiTopk, 2u, epi_args.mask_tma != 0, pairs, EPI == kEpiSoftmax);
+  if (dual && !(EPI == kEpiMin && presplit && a_resident && !pairs && 2 * kblocks <= kMaxResidentKBlocks))
+    return fail(FBMM_ERR_INVALID, "internal: two resident row blocks need the pre-split min kernel and K <= 64");
+  const SmemPlan plan = make_smem_plan(a_resident, dual ? 2 * kblocks : kblocks, EPI == kEpiTopk, 2u, epi_args.mask_tma != 0, pairs,
+                                       EPI == kEpiSoftmax);
   if (plan.stages < 2) return fail(FBMM_ERR_INVALID, "internal: shared-memory plan has %u stages", plan.stages);
   // min / top-k have pre-split variants; store / mask never use them
   constexpr bool kHasPresplit = (EPI == kEpiMin || EPI == kEpiTopk);
@@ -537,7 +553,11 @@ int launch_gemm(cudaStream_t stream, const DeviceState& st, const RowProblem& p,
   cfg.numAttrs = 1;
 #define FBMM_LAUNCH(AR, PS, PR) \
   FBMM_CUDA(cudaLaunchKernelEx(&cfg, fbmm_gemm_kernel<EPI, E, AR, PS, 0, PR>, ta, tb, ta_lo, tb_lo, tem, ttm, shape, epi_args))
-  if (ps && pairs) {
+  if (dual) {
+    constexpr bool kMin = EPI == kEpiMin;  // (the only epilogue with this variant)
+    FBMM_CUDA(cudaLaunchKernelEx(&cfg, fbmm_gemm_kernel<EPI, E, true, kMin, 0, false, kMin>, ta, tb, ta_lo, tb_lo, tem, ttm, shape,
+                                 epi_args));
+  } else if (ps && pairs) {
     if (a_resident) FBMM_LAUNCH(true, kHasPresplit, kHasPresplit); else FBMM_LAUNCH(false, kHasPresplit, kHasPresplit);
   } else if (a_resident) {
     if (ps) FBMM_LAUNCH(true, kHasPresplit, false); else FBMM_LAUNCH(true, false, false);
@@ -720,7 +740,9 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
   const bool presplit = !l1 && presplit_worthwhile(p) && (b_planes_fit_l2(p) || p.L == 1) &&
                         workspace_bytes >= lo_off + presplit_bytes(p);
   const bool pairs = pairs_apply(p, presplit);
-  GemmShape s = base_shape(p, pairs);
+  // K <= 64 on pre-split planes: two resident row blocks of A per CTA share every B stage
+  const bool dual = dual_rows_apply(p, presplit) && !pairs;
+  GemmShape s = base_shape(p, pairs || dual);
   // (an l1 tile costs so many fp32 instructions that an extra unit costs nothing beside it: the
   // column sweep is cut as finely as balances the 2 x sms CTAs best)
   choose_chunks(l, s.m_blocks, s.n_tiles, l1 ? 2 * st->sms : unit_workers(st->sms, pairs), l1 ? 0 : kMinOverheadTiles,
@@ -754,7 +776,7 @@ int fbmm_min_bmm_f32(void* stream_, const float* A, int a_layout, long long lda,
     }
   }
   if (l1) rc = launch_l1<kEpiMin, 1>(stream, *st, p, s, e);
-  else rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e, lo_scratch, pairs);
+  else rc = launch_gemm<kEpiMin, 1>(stream, *st, p, s, e, lo_scratch, pairs, dual);
   if (rc != FBMM_OK) return rc;
   const int threads = 256;
   const long long blocks = (rows + threads - 1) / threads;

@@ -726,7 +726,16 @@ __device__ __forceinline__ void split_plane(const uint8_t* hi, uint8_t* lo, uint
 // row), there are no lo planes and nothing to split, so these variants are instantiated with
 // PRESPLIT = true and load the hi planes only. Both operands must be k-contiguous. The
 // lo-plane slots of the shared-memory plan stay unused.
-template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT, int DT = 0, bool PAIR = false>
+//
+// DUAL: two resident row blocks of A per CTA (a 256-row unit) take turns on the two accumulator
+// stages, so that every ring stage of B serves 256 rows before it is released: half the operand
+// bytes per output pulled out of L2 into the SM, which is what bounds the K <= 64 kernels (with
+// the MMAs, the accumulator loads and the epilogue arithmetic compiled out they still took three
+// quarters of their time). The ring walks real column tiles; the MMA thread and the epilogue walk
+// "virtual tiles" (column tile, row block), row block 0 always on accumulator stage 0. A stage is
+// waited for by the first row block and released by the second. Needs both blocks' hi and lo
+// planes resident (2 x kblocks <= 4 slots: K <= 64), B's planes by TMA, a single CTA; min epilogue.
+template <int EPI, int TOPK_E, bool A_RES, bool PRESPLIT, int DT = 0, bool PAIR = false, bool DUAL = false>
 __global__ void __launch_bounds__(block_threads(EPI), 1)
 fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_a_lo, const __grid_constant__ CUtensorMap tmap_b_lo,
@@ -740,12 +749,15 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   static_assert(!kHalf || PRESPLIT, "16-bit variants: PRESPLIT = true");
   static_assert(!PAIR || (PRESPLIT && !kHalf && (EPI == kEpiMin || EPI == kEpiTopk)),
                 "pair variants: fp32 operands with pre-split planes, reducing epilogues");
+  static_assert(!DUAL || (EPI == kEpiMin && A_RES && PRESPLIT && !PAIR && !kHalf),
+                "dual row blocks: min epilogue, A resident, pre-split planes, single CTA, fp32");
+  constexpr int kRb = DUAL ? 2 : 1;  // row blocks of A a CTA keeps resident
   constexpr int kKElems = kHalf ? 2 * kKBlock : kKBlock;  // elements of K per k-block (128 bytes)
   const int kblocks = (shape.K + kKElems - 1) / kKElems;
   constexpr uint32_t kPlanes = kHalf ? 1u : 2u;  // planes per operand tile in shared memory
   const bool mask_tma = is_masked(EPI) && epi.mask_tma != 0;
   constexpr int kSweeps = sweeps(EPI);
-  const SmemPlan plan = make_smem_plan(A_RES, kblocks, EPI == kEpiTopk, kPlanes, mask_tma, PAIR, EPI == kEpiSoftmax);
+  const SmemPlan plan = make_smem_plan(A_RES, kblocks * kRb, EPI == kEpiTopk, kPlanes, mask_tma, PAIR, EPI == kEpiSoftmax);
   const uint32_t stages = plan.stages;
   constexpr uint32_t kBPlane = kPlaneBytes;  // one plane of a B tile
   // offsets inside a ring stage. Single CTA: (A hi | A lo |) B hi | B lo. Pair: (A hi | A lo |)
@@ -825,7 +837,10 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const long long unit_first = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
   const long long unit_step = PAIR ? (gridDim.x >> 1) : gridDim.x;
   // first row of this CTA inside row block `mb` (row blocks are 256 rows for pairs)
-  auto row_base = [&](int mb) -> int { return PAIR ? mb * 2 * kTileM + static_cast<int>(cta_rank) * kTileM : mb * kTileM; };
+  // (with DUAL a unit is 256 rows too; its second row block starts kTileM rows further on)
+  auto row_base = [&](int mb) -> int {
+    return PAIR ? mb * 2 * kTileM + static_cast<int>(cta_rank) * kTileM : (DUAL ? mb * 2 * kTileM : mb * kTileM);
+  };
 
   // Decodes unit u into batch, row block and column-tile range.
   auto decode = [&](long long u, int& b, int& mb, int& t0, int& t1) {
@@ -867,14 +882,15 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     else tma_load_3d(dst, map, bar, c0, c1, c2, policy);
   };
   // this CTA's 128 rows of A of row block mb, k-block kb
-  auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int mb, int b) {
+  auto load_a = [&](const CUtensorMap* map, uint8_t* dst, uint64_t* bar, bool to_leader, int kb, int mb, int b,
+                    int row_off = 0) {
     if (shape.a_bcast) b = 0;
     if (!shape.a_mn) {
-      tma_issue(dst, map, bar, to_leader, kb * kKElems, row_base(mb), b, a_policy);
+      tma_issue(dst, map, bar, to_leader, kb * kKElems, row_base(mb) + row_off, b, a_policy);
     } else {
 #pragma unroll
       for (int c = 0; c < kTileM / 32; ++c)
-        tma_issue(dst + c * 4096, map, bar, to_leader, row_base(mb) + c * 32, kb * kKBlock, b, a_policy);
+        tma_issue(dst + c * 4096, map, bar, to_leader, row_base(mb) + row_off + c * 32, kb * kKBlock, b, a_policy);
     }
   };
   // `ncols` columns (a multiple of 32) of an operand plane of B starting at column `col`, k-block kb.
@@ -1052,6 +1068,11 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int sweep = 0; sweep < kSweeps; ++sweep)
         for (int t = first; t <= last && ok; ++t) {
           if (!tile_live(b, mb, t)) continue;
+          // (DUAL: the tile's ring stages are walked once per row block, from the same start)
+          const uint32_t stage_t = stage, phase_t = phase;
+          for (int rb = 0; rb < kRb && ok; ++rb) {
+          stage = stage_t;
+          phase = phase_t;
           FBMM_TRACE(0);
           FBMM_PROF_BEGIN();
           ok = wait_gate(&bars->acc_empty[acc_stage], acc_phase ^ 1u);
@@ -1061,22 +1082,25 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t acc_big = tmem_base + acc_stage * (2 * TILE_N);
           const uint32_t acc_small = acc_big + TILE_N;
           for (int kb = 0; kb < kblocks; ++kb) {
+            const int a_slot = rb * kblocks + kb;  // resident slot of this row block's k-block
             if (A_RES && t == first && sweep == 0) {
               // 16-bit operands are used as they land; fp32 ones once their lo plane exists
               FBMM_PROF_BEGIN();
-              ok = wait_gate(kHalf ? &bars->a_full[kb] : &bars->a_split[kb], a_phase);
+              ok = wait_gate(kHalf ? &bars->a_full[a_slot] : &bars->a_split[a_slot], a_phase);
               FBMM_PROF_END(3);
               if (!ok) break;
             }
-            FBMM_PROF_BEGIN();
-            ok = wait_gate(PRESPLIT ? &bars->full[stage] : &bars->split[stage], phase);
-            FBMM_PROF_END(1);
-            if (!ok) break;
+            if (rb == 0) {  // (the second row block finds the stage as the first left it)
+              FBMM_PROF_BEGIN();
+              ok = wait_gate(PRESPLIT ? &bars->full[stage] : &bars->split[stage], phase);
+              FBMM_PROF_END(1);
+              if (!ok) break;
+            }
             // (no tcgen05 fence here: the operands reach shared memory through the async
             // proxy, or through writers that ran fence.proxy.async before arriving)
             FBMM_PROF_BEGIN();
             const uint32_t sb = smem_u32(ring + stage * plan.stage_bytes);
-            const uint32_t sa = A_RES ? smem_u32(a_region + kb * kPlanes * kPlaneBytes) : sb;
+            const uint32_t sa = A_RES ? smem_u32(a_region + a_slot * kPlanes * kPlaneBytes) : sb;
             // Issue order: all four k-steps of one operand-plane combination before the
             // next combination, so that consecutive MMAs walk the same 128-byte
             // shared-memory rows.
@@ -1112,14 +1136,15 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                           1u);
               (void)b_lo0;
             }
-            commit_all(&bars->empty[stage]);
-            if (A_RES && t == last && sweep == kSweeps - 1) commit_all(&bars->a_empty[kb]);
+            if (rb == kRb - 1) commit_all(&bars->empty[stage]);  // the last row block releases the stage
+            if (A_RES && t == last && sweep == kSweeps - 1) commit_all(&bars->a_empty[a_slot]);
             FBMM_PROF_END(2);
             if (++stage == stages) { stage = 0; phase ^= 1u; }
           }
           if (!ok) break;
           commit_all(&bars->acc_full[acc_stage]);
           if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
+          }  // row blocks
         }
         a_phase ^= 1u;
       }
@@ -1142,7 +1167,7 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (int t = first; t <= last && ok; ++t) {
         if (!tile_live(b, mb, t)) continue;
         if (PRESPLIT && (t != first || sweep != 0)) break;  // only the unit's resident A block needs splitting
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int kb = 0; kb < (DUAL ? 2 * kblocks : kblocks); ++kb) {  // (DUAL: kb counts resident slots)
           if (A_RES && t == first && sweep == 0) {
             ok = mbar_wait(&bars->a_full[kb], a_phase, abort_flag);
             if (!ok) break;
@@ -1203,10 +1228,16 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
       // squared-l2 mode: this row's squared norm
       const bool l2 = (EPI == kEpiMin || EPI == kEpiTopk) && epi.row_norms != nullptr;
-      const float row_norm = (l2 && row_ok) ? epi.row_norms[static_cast<long long>(b) * shape.M + row] : 0.f;
+      float row_norm = (l2 && row_ok) ? epi.row_norms[static_cast<long long>(b) * shape.M + row] : 0.f;
       // per-unit reduction state
       float best = INFINITY;
       int best_col = t0 * TILE_N;
+      // DUAL: the same for this thread's row of the unit's second row block (row + kTileM); the two
+      // sets change places around every virtual tile of that block
+      const bool row_ok_o = DUAL && row + kTileM < shape.M;
+      float row_norm_o = (DUAL && l2 && row_ok_o) ? epi.row_norms[static_cast<long long>(b) * shape.M + row + kTileM] : 0.f;
+      float best_o = INFINITY;
+      int best_col_o = t0 * TILE_N;
       // top-k: current k-th best of this row (+inf for rows past M, which never stage)
       float thr = row_ok ? -INFINITY : INFINITY;
       const uint32_t stg_base = smem_u32(stg + row_in_tile);
@@ -1255,8 +1286,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
       }
       for (int t = t0; t < t1 && ok; ++t) {
+      for (int rb = 0; rb < kRb && ok; ++rb) {  // (one pass unless DUAL)
+        if (DUAL && rb == 1) {
+          float tf = best; best = best_o; best_o = tf;
+          int ti = best_col; best_col = best_col_o; best_col_o = ti;
+          tf = row_norm; row_norm = row_norm_o; row_norm_o = tf;
+        }
         const int col_tile = t * TILE_N;
-                FBMM_TRACE_TAG(3, 0);
+        FBMM_TRACE_TAG(3, 0);
         const bool live = tile_live(b, mb, t);
         if (live) { FBMM_TRACE_TAG(3, 1); }  // loads and MMAs happen for this tile
         if (!live) {
@@ -1640,6 +1677,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (threadIdx.x == 192) { FBMM_TRACE(1); }
         if (++acc_stage == kAccStages) { acc_stage = 0; acc_phase ^= 1u; }
         if (mask_tma && ++mstage == kMaskStages) { mstage = 0; mphase ^= 1u; }
+        if (DUAL && rb == 1) {
+          float tf = best; best = best_o; best_o = tf;
+          int ti = best_col; best_col = best_col_o; best_col_o = ti;
+          tf = row_norm; row_norm = row_norm_o; row_norm_o = tf;
+        }
+      }  // row blocks
       }
       }  // sweeps
 
@@ -1650,6 +1693,12 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const unsigned long long key =
               (static_cast<unsigned long long>(float_to_ordered(bz)) << 32) | static_cast<uint32_t>(best_col);
           atomicMin(epi.keys + static_cast<long long>(b) * shape.M + row, key);
+        }
+        if (DUAL && row_ok_o && ok) {
+          const float bz = best_o + 0.0f;
+          const unsigned long long key =
+              (static_cast<unsigned long long>(float_to_ordered(bz)) << 32) | static_cast<uint32_t>(best_col_o);
+          atomicMin(epi.keys + static_cast<long long>(b) * shape.M + row + kTileM, key);
         }
       } else if (EPI == kEpiTopk) {
         if (ok) {
@@ -1672,12 +1721,14 @@ fbmm_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int b, mb, t0, t1, first, last;
         decode(u, b, mb, t0, t1);
         if (!live_range( b, mb, t0, t1, first, last)) continue;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        for (int slot = 0; slot < kblocks * kRb && ok; ++slot) {  // slot = row block * kblocks + k-block
+          const int rb = slot / kblocks, kb = slot - rb * kblocks;
           // free as soon as the previous unit's last tile has finished with that k-block
-          ok = wait_gate(&bars->a_empty[kb], a_phase ^ 1u);
+          ok = wait_gate(&bars->a_empty[slot], a_phase ^ 1u);
           if (!ok) break;
-          mbar_arrive_expect_tx(&bars->a_full[kb], kPlaneBytes);
-          load_a(&tmap_a, a_region + kb * kPlanes * kPlaneBytes + off_a_hi, &bars->a_full[kb], false, kb, mb, b);
+          mbar_arrive_expect_tx(&bars->a_full[slot], kPlaneBytes);
+          load_a(&tmap_a, a_region + slot * kPlanes * kPlaneBytes + off_a_hi, &bars->a_full[slot], false, kb, mb, b,
+                 rb * kTileM);
         }
         a_phase ^= 1u;
       }
