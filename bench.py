@@ -429,7 +429,7 @@ def algorithmic_bytes(name, units, n_cols):
 #   c5: 37 888 rows = two waves of 74 CTA pairs; every wave streams B's planes (2 x 1 GiB) from
 #       DRAM once, so the traffic grows with the number of waves: bytes per row = capture / rows.
 TRAFFIC_CAPTURES = {
-    "c1": (16384, 0.0, 12766464.0 + 0.0),
+    "c1": (16384, 0.0, 12771840.0 + 0.0),
     "c2": (128, 0.0, 142640640.0 + 477262080.0),
     "c3": (128, 0.0, 202073344.0 + 478761728.0),
     "c4": (262144, 2.0 * 128 * 65536 * 4, 356611840.0 + 5492992.0 - 2.0 * 128 * 65536 * 4),
