@@ -31,8 +31,9 @@
 //
 // Variants (template parameters of the kernel): lo planes taken from global memory
 // instead of the splitters (PRESPLIT), clusters of two CTAs on 256-row blocks with
-// tcgen05.mma.cta_group::2 (PAIR; min and top-k on pre-split planes, K > 64), and fp16 / bf16
-// operands multiplied as they are by kind::f16 (DT).
+// tcgen05.mma.cta_group::2 (PAIR; min and top-k on pre-split planes, K > 64), two resident row
+// blocks of A per CTA sharing every B stage (DUAL; min on pre-split planes, K <= 64), and fp16 /
+// bf16 operands multiplied as they are by kind::f16 (DT).
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
