@@ -369,7 +369,10 @@ def test_presplit_scratch_gives_identical_bits(dev, lib):
     in a single bit (min and top-k with K <= 128 and K > 128)."""
     g = torch.Generator().manual_seed(31)
     stream = torch.cuda.current_stream().cuda_stream
-    for (m, k, n) in [(1100, 96, 1300), (1024, 160, 1536), (1280, 128, 1100)]:
+    # (K <= 64 with pre-split planes is the min kernel with two resident row blocks of A per CTA:
+    # 1100 rows leave its last unit a ragged second block, 1408 an absent one, K = 20 one k-block)
+    for (m, k, n) in [(1100, 96, 1300), (1024, 160, 1536), (1280, 128, 1100), (1100, 64, 1300), (1408, 20, 1024),
+                      (2048, 36, 2500)]:
         A = torch.randn(1, m, k, generator=g).to(dev)
         B = torch.randn(1, k, n, generator=g).to(dev)
         extra = lib.fbmm_presplit_workspace_bytes(1, m, n, k, 2, ord("n"), k, m * k, ord("n"), n, k * n)
@@ -400,6 +403,28 @@ def test_presplit_scratch_gives_identical_bits(dev, lib):
         R.check_topk(outs[1][2], outs[1][3], A.cpu(), B.cpu(), 16, 2)
     assert lib.fbmm_presplit_workspace_bytes(1, 512, 4096, 64, 2, ord("n"), 64, 0, ord("n"), 4096, 0) == 0
     assert lib.fbmm_check(None) == 0, lib.fbmm_last_error()
+
+
+def test_two_row_block_min_kernel_l2_and_dim1(dev, lib):
+    """The K <= 64 min kernel on pre-split planes (two resident row blocks per CTA) through the
+    wrapper, which passes the planes' scratch: squared-l2 distance, both dims, a transposed
+    layout, batches; against the oracle, and exact integers bit for bit."""
+    from custom_matmul_kernels_b200 import MinBMMCUDA
+    g = torch.Generator().manual_seed(77)
+    A, B = torch.randn(2, 1300, 48, generator=g), torch.randn(2, 48, 1200, generator=g)
+    Ad, Bd = A.to(dev), B.to(dev)
+    Bt = Bd.transpose(1, 2).contiguous().transpose(1, 2)
+    for distance in ("inner", "l2"):
+        op = MinBMMCUDA(distance=distance)
+        for dim in (1, 2):
+            for b_ in (Bd, Bt):
+                v, i = op(Ad, b_, dim=dim)
+                R.check_min(v, i, A, B, dim, distance=distance)
+    Ae, Be = R.exact_inputs(1, 1536, 64, 1024, seed=9)
+    v, i = MinBMMCUDA()(Ae.to(dev), Be.to(dev), dim=2)
+    wv, wi = R.min_bmm(Ae, Be, dim=2)
+    assert torch.equal(v.cpu(), wv) and torch.equal(i.cpu(), wi)
+    device_ok(lib)
 
 
 def test_topk_and_min_with_pre_split_planes_wider_than_l2(dev, lib):
